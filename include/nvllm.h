@@ -188,19 +188,30 @@ int nvllm_create(const nvllm_config* cfg, const uint8_t* tp_id, nvllm_handle** o
  *                                   x += mixer(h) + feed_forward(h)                   (Dugopel)
  *   NVLLM_LBLOCK_SEQUENTIAL_POSTNORM  x += RMSNorm(mixer(x)), then x += RMSNorm(feed_forward(x)):
  *                                   the sublayers read x itself, the norm sits on their output (Zozonex)
+ *   NVLLM_LBLOCK_SEQUENTIAL_PRENORM   x += mixer(RMSNorm(x)), then x += feed_forward(RMSNorm(x)); a run of
+ *                                   layers may repeat with the same weights (loop_*), every pass with caches and
+ *                                   state of its own and a learned vector added to x at its start       (Lazovik)
  * Tensors are handed in by checkpoint name (nvllm_set_named_weight, or nvllm_load_safetensors
- * with NVLLM_ARCH_DUGOPEL / NVLLM_ARCH_ZOZONEX). */
+ * with NVLLM_ARCH_DUGOPEL / NVLLM_ARCH_ZOZONEX / NVLLM_ARCH_LAZOVIK). */
 enum nvllm_mixer_kind {
   NVLLM_MIXER_LATENT_ATTENTION = 1,
   NVLLM_MIXER_WINDOW_ATTENTION = 2, /* grouped-query attention over a sliding window of the paged K / V cache */
-  NVLLM_MIXER_DELTA = 3             /* gated delta rule: a recurrent dim x vdim state per head, kept per state slot */
+  NVLLM_MIXER_DELTA = 3,            /* gated delta rule: a recurrent dim x vdim state per head, kept per state slot */
+  NVLLM_MIXER_GLA = 4,              /* gated linear attention: S <- diag(alpha) S + k v^T, o = S^T q, state per slot */
+  NVLLM_MIXER_ATTN_TMIX = 5         /* two mixers on one input, their outputs summed with two scales: grouped-query
+                                       attention (short convolution, whole-row q / k norm, rotation, score cap, chunked
+                                       mask, output gate) and time mixing with a token shift (heads2 x dim2) */
 };
 enum nvllm_mlp_kind { NVLLM_MLP_NONE = 0, NVLLM_MLP_DENSE = 1, NVLLM_MLP_MOE = 2 };
 enum nvllm_ffn_act {
   NVLLM_FFN_GLU_CLAMPED = 0, /* W_down (g sigmoid(1.702 g) (u + 1)), g / u clamped by `limit` */
   NVLLM_FFN_RELU2 = 1        /* W_down relu(W_up h)^2 */
 };
-enum nvllm_layered_block { NVLLM_LBLOCK_PARALLEL_PRENORM = 0, NVLLM_LBLOCK_SEQUENTIAL_POSTNORM = 1 };
+enum nvllm_layered_block {
+  NVLLM_LBLOCK_PARALLEL_PRENORM = 0,
+  NVLLM_LBLOCK_SEQUENTIAL_POSTNORM = 1,
+  NVLLM_LBLOCK_SEQUENTIAL_PRENORM = 2 /* x += mixer(RMSNorm(x)), then x += feed_forward(RMSNorm(x)) (Lazovik) */
+};
 enum nvllm_layered_position { NVLLM_LPOS_NONE = 0, NVLLM_LPOS_SINUSOIDAL = 1 };
 
 typedef struct nvllm_layer_spec {
@@ -227,6 +238,25 @@ typedef struct nvllm_layer_spec {
   int32_t qk_norm;      /* window attention: 1 = q and k divided by their root mean square per head (eps of the model) */
   int32_t conv;         /* delta rule: taps of the causal convolution over time on q, k, v */
   int32_t act;          /* dense feed-forward: nvllm_ffn_act */
+  /* attention side of NVLLM_MIXER_ATTN_TMIX (uses heads, kv_heads, dim, vdim, scale, conv, rot_base, rot_dims,
+   * qk_norm = 2: RMS norm over the whole q / k row with a weight) */
+  int32_t chunk;        /* position i sees j <= i only when i / chunk == j / chunk; 0 = off */
+  float softcap;        /* score <- softcap * tanh(score / softcap); 0 = off */
+  int32_t proj_bias;    /* 1: q, k, v and the output projection have biases */
+  int32_t out_gate;     /* 1: the heads' outputs are multiplied by sigmoid(W_g h) before the output projection */
+  /* frequency interpolation of the rotation (rot_factor > 0): between the entries whose wavelength is
+   * rot_original / rot_fast and rot_original / rot_slow the frequency goes from f to f / rot_factor, and
+   * cos / sin are multiplied by 0.1 ln(rot_factor) + 1 */
+  float rot_factor, rot_original, rot_fast, rot_slow;
+  /* recurrent sides */
+  float tau;            /* gated linear attention: decay = sigmoid(z)^(1 / tau) */
+  int32_t lowrank;      /* inner size of the decay's two-step projection */
+  int32_t heads2, dim2; /* NVLLM_MIXER_ATTN_TMIX: heads and entries per head of the time-mixing side */
+  float mix_scale, mix2_scale; /* NVLLM_MIXER_ATTN_TMIX: result = mix_scale * attention + mix2_scale * time mixing */
+  /* mixture of experts with act = NVLLM_FFN_RELU2 */
+  int32_t route_sigmoid;   /* 1: scores are sigmoid(logits) instead of a softmax over the experts */
+  int32_t weight_on_input; /* 1: the routing weight multiplies the expert's input instead of its output */
+  int32_t shared_ff;       /* > 0: one more expert of this inner size runs for every token, times sigmoid(W_sg h) */
 } nvllm_layer_spec;
 
 typedef struct nvllm_layered_config {
@@ -242,6 +272,9 @@ typedef struct nvllm_layered_config {
   int32_t tied_head;       /* 1: logits = embed x (the table itself, without embedding_scale); no "head" tensor */
   float norm_offset;       /* norm weights are stored as w - norm_offset (1: "around zero") */
   int32_t num_state_slots; /* recurrent mixers: sequences that can hold state at once (<= 0: max_num_seqs) */
+  /* layers [loop_start, loop_stop) run loop_times times in a row with the same weights (loop_times <= 1: once);
+   * tensor "loop.step" [loop_times, hidden]: row t is added to x before pass t */
+  int32_t loop_start, loop_stop, loop_times;
 } nvllm_layered_config;
 
 int nvllm_create_layered(const nvllm_layered_config* cfg, const nvllm_layer_spec* layers,
@@ -285,7 +318,8 @@ enum nvllm_arch {
   NVLLM_ARCH_LLAMA = 2,       /* GetLlamaMapping: separate q/k/v, gate_proj + up_proj */
   NVLLM_ARCH_GRANITE_MOE = 3, /* GetGraniteMoEMapping: router + stacked expert tensors */
   NVLLM_ARCH_DUGOPEL = 4,     /* layered handle: every tensor of the file by its own name */
-  NVLLM_ARCH_ZOZONEX = 5      /* layered handle, likewise */
+  NVLLM_ARCH_ZOZONEX = 5,     /* layered handle, likewise */
+  NVLLM_ARCH_LAZOVIK = 6      /* layered handle, likewise */
 };
 
 /* Load every weight of the model straight from `model_dir` — model.safetensors, or the shards

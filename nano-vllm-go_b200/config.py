@@ -26,11 +26,11 @@ ACT_GELU, ACT_SWIGLU = 0, 1
 BLOCK_SEQUENTIAL, BLOCK_PARALLEL = 0, 1
 PREC_FP32, PREC_BF16 = 0, 1
 # enum nvllm_arch (checkpoint families of generic_loader.go:60-182)
-ARCH_GPT2, ARCH_FALCON, ARCH_LLAMA, ARCH_GRANITE_MOE, ARCH_DUGOPEL, ARCH_ZOZONEX = 0, 1, 2, 3, 4, 5
-MIXER_LATENT_ATTENTION, MIXER_WINDOW_ATTENTION, MIXER_DELTA = 1, 2, 3
+ARCH_GPT2, ARCH_FALCON, ARCH_LLAMA, ARCH_GRANITE_MOE, ARCH_DUGOPEL, ARCH_ZOZONEX, ARCH_LAZOVIK = 0, 1, 2, 3, 4, 5, 6
+MIXER_LATENT_ATTENTION, MIXER_WINDOW_ATTENTION, MIXER_DELTA, MIXER_GLA, MIXER_ATTN_TMIX = 1, 2, 3, 4, 5
 MLP_NONE, MLP_DENSE, MLP_MOE = 0, 1, 2
 FFN_GLU_CLAMPED, FFN_RELU2 = 0, 1
-LBLOCK_PARALLEL_PRENORM, LBLOCK_SEQUENTIAL_POSTNORM = 0, 1
+LBLOCK_PARALLEL_PRENORM, LBLOCK_SEQUENTIAL_POSTNORM, LBLOCK_SEQUENTIAL_PRENORM = 0, 1, 2
 LPOS_NONE, LPOS_SINUSOIDAL = 0, 1
 DT_F32, DT_BF16, DT_F16 = 0, 1, 2
 
@@ -302,6 +302,13 @@ class CLayerSpec(ctypes.Structure):
         ("router_scale", ctypes.c_float),
         ("kv_heads", ctypes.c_int32), ("window", ctypes.c_int32), ("sink", ctypes.c_int32),
         ("qk_norm", ctypes.c_int32), ("conv", ctypes.c_int32), ("act", ctypes.c_int32),
+        ("chunk", ctypes.c_int32), ("softcap", ctypes.c_float), ("proj_bias", ctypes.c_int32),
+        ("out_gate", ctypes.c_int32),
+        ("rot_factor", ctypes.c_float), ("rot_original", ctypes.c_float), ("rot_fast", ctypes.c_float),
+        ("rot_slow", ctypes.c_float),
+        ("tau", ctypes.c_float), ("lowrank", ctypes.c_int32), ("heads2", ctypes.c_int32), ("dim2", ctypes.c_int32),
+        ("mix_scale", ctypes.c_float), ("mix2_scale", ctypes.c_float),
+        ("route_sigmoid", ctypes.c_int32), ("weight_on_input", ctypes.c_int32), ("shared_ff", ctypes.c_int32),
     ]
 
 
@@ -317,6 +324,7 @@ class CLayeredConfig(ctypes.Structure):
         ("device", ctypes.c_int32),
         ("block_style", ctypes.c_int32), ("position", ctypes.c_int32), ("tied_head", ctypes.c_int32),
         ("norm_offset", ctypes.c_float), ("num_state_slots", ctypes.c_int32),
+        ("loop_start", ctypes.c_int32), ("loop_stop", ctypes.c_int32), ("loop_times", ctypes.c_int32),
     ]
 
 
@@ -349,6 +357,23 @@ class LayerSpec:
     qk_norm: int = 0
     conv: int = 0
     act: int = FFN_GLU_CLAMPED
+    chunk: int = 0
+    softcap: float = 0.0
+    proj_bias: int = 0
+    out_gate: int = 0
+    rot_factor: float = 0.0
+    rot_original: float = 0.0
+    rot_fast: float = 0.0
+    rot_slow: float = 0.0
+    tau: float = 0.0
+    lowrank: int = 0
+    heads2: int = 0
+    dim2: int = 0
+    mix_scale: float = 1.0
+    mix2_scale: float = 1.0
+    route_sigmoid: int = 0
+    weight_on_input: int = 0
+    shared_ff: int = 0
 
     def to_c(self) -> CLayerSpec:
         c = CLayerSpec()
@@ -359,6 +384,8 @@ class LayerSpec:
     def tensor_shapes(self, layer: int, width: int) -> dict:
         """Checkpoint names and shapes of this layer's tensors (linears [out, in])."""
         p = f"l{layer}."
+        if self.mixer in (MIXER_GLA, MIXER_ATTN_TMIX):
+            return self._prenorm_shapes(p, width)
         if self.mixer == MIXER_WINDOW_ATTENTION:
             d = {p + "norm1": (width,), p + "mix.q": (self.heads * self.dim, width),
                  p + "mix.o": (width, self.heads * self.vdim)}
@@ -397,9 +424,46 @@ class LayerSpec:
         return d
 
 
+def _prenorm_shapes(self, p: str, width: int) -> dict:
+    hd, hv = self.heads * self.dim, self.heads * self.vdim
+    d = {p + "norm1": (width,)}
+    if self.mixer == MIXER_GLA:
+        d.update({p + "mix.q": (hd, width), p + "mix.k": (hd, width), p + "mix.v": (hv, width),
+                  p + "mix.g": (hv, width), p + "mix.o": (width, hv), p + "mix.norm": (self.vdim,),
+                  p + "mix.a1": (self.lowrank, width), p + "mix.a2": (hd, self.lowrank), p + "mix.a2.b": (hd,)})
+    else:
+        m = p + "mix.left."
+        nk, nv = self.kv_heads * self.dim, self.kv_heads * self.vdim
+        d.update({m + "q": (hd, width), m + "k": (nk, width), m + "v": (nv, width),
+                  m + "q.norm": (hd,), m + "k.norm": (nk,), m + "q.conv": (hd, self.conv),
+                  m + "k.conv": (nk, self.conv), m + "v.conv": (nv, self.conv), m + "o": (width, hv)})
+        if self.proj_bias:
+            d.update({m + "q.b": (hd,), m + "k.b": (nk,), m + "v.b": (nv,), m + "o.b": (width,)})
+        if self.out_gate:
+            d[m + "g"] = (hv, width)
+        m = p + "mix.right."
+        hd2 = self.heads2 * self.dim2
+        d.update({m + "mu." + x: (width,) for x in "rkvgw"})
+        d.update({m + "r": (hd2, width), m + "k": (hd2, width), m + "v": (hd2, width), m + "g": (hd2, width),
+                  m + "w1": (self.lowrank, width), m + "w2": (hd2, self.lowrank), m + "w0": (hd2,),
+                  m + "u": (self.heads2, self.dim2), m + "norm": (hd2,), m + "o": (width, hd2)})
+    if self.mlp == MLP_MOE:
+        d[p + "norm2"] = (width,)
+        d[p + "mlp.router"] = (self.experts, width)
+        for e in range(self.experts):
+            d.update({f"{p}mlp.e{e}.up": (self.ff, width), f"{p}mlp.e{e}.down": (width, self.ff)})
+        if self.shared_ff > 0:
+            d.update({p + "mlp.shared.up": (self.shared_ff, width), p + "mlp.shared.down": (width, self.shared_ff),
+                      p + "mlp.shared.sg": (1, width)})
+    return d
+
+
+LayerSpec._prenorm_shapes = _prenorm_shapes
+
+
 @dataclass(frozen=True)
 class ListedModelConfig:
-    """A model whose config.json lists its layers (architectures "Dugopel", "Zozonex")."""
+    """A model whose config.json lists its layers (architectures "Dugopel", "Zozonex", "Lazovik")."""
     name: str
     vocab_size: int
     hidden: int
@@ -413,6 +477,18 @@ class ListedModelConfig:
     position: int = LPOS_NONE
     tied_head: bool = False
     norm_offset: float = 0.0
+    loop_start: int = 0
+    loop_stop: int = 0
+    loop_times: int = 1
+
+    @property
+    def runs(self) -> Tuple[int, ...]:
+        """Layer indices in execution order (a repeated run of layers counts every pass)."""
+        n = len(self.layers)
+        if self.loop_times <= 1:
+            return tuple(range(n))
+        return tuple(range(self.loop_start)) + tuple(range(self.loop_start, self.loop_stop)) * self.loop_times + \
+            tuple(range(self.loop_stop, n))
 
     @property
     def num_layers(self) -> int:
@@ -421,12 +497,14 @@ class ListedModelConfig:
     @property
     def needs_state_slots(self) -> bool:
         """True when some layer keeps recurrent state per sequence (delta rule)."""
-        return any(l.mixer == MIXER_DELTA for l in self.layers)
+        return any(l.mixer in (MIXER_DELTA, MIXER_GLA, MIXER_ATTN_TMIX) for l in self.layers)
 
     def tensor_shapes(self) -> dict:
         d = {"embed": (self.vocab_size, self.hidden), "final.norm": (self.hidden,)}
         if not self.tied_head:
             d["head"] = (self.vocab_size, self.hidden)
+        if self.loop_times > 1:
+            d["loop.step"] = (self.loop_times, self.hidden)
         for i, l in enumerate(self.layers):
             d.update(l.tensor_shapes(i, self.hidden))
         return d
@@ -438,8 +516,10 @@ class ListedModelConfig:
 
     def cache_bytes_per_token(self, bytes_per_el: int = 2) -> int:
         n = 0
-        for l in self.layers:
-            if l.mixer == MIXER_LATENT_ATTENTION and l.kv_from < 0:
+        for l in (self.layers[i] for i in self.runs):
+            if l.mixer == MIXER_ATTN_TMIX:
+                n += l.kv_heads * (l.dim + l.vdim) * bytes_per_el
+            elif l.mixer == MIXER_LATENT_ATTENTION and l.kv_from < 0:
                 n += (l.kv_rank + l.rot_dim) * bytes_per_el
             elif l.mixer == MIXER_WINDOW_ATTENTION and l.kv_from < 0:
                 n += l.kv_heads * (l.dim + l.vdim) * bytes_per_el
@@ -447,8 +527,15 @@ class ListedModelConfig:
 
     def state_bytes_per_sequence(self) -> int:
         """fp32 recurrent state + convolution tail of the delta-rule layers."""
-        return sum(4 * (l.heads * l.dim * l.vdim + (l.conv - 1) * (2 * l.kv_heads * l.dim + l.heads * l.vdim))
-                   for l in self.layers if l.mixer == MIXER_DELTA)
+        n = sum(4 * (l.heads * l.dim * l.vdim + (l.conv - 1) * (2 * l.kv_heads * l.dim + l.heads * l.vdim))
+                for l in self.layers if l.mixer == MIXER_DELTA)
+        for l in (self.layers[i] for i in self.runs):
+            if l.mixer == MIXER_GLA:
+                n += 4 * l.heads * l.dim * l.vdim
+            elif l.mixer == MIXER_ATTN_TMIX:
+                n += 4 * (l.heads2 * l.dim2 * l.dim2 + self.hidden +
+                          (l.conv - 1) * (l.heads * l.dim + l.kv_heads * (l.dim + l.vdim)))
+        return n
 
     def to_c(self, precision: int, num_kv_blocks: int = -1, max_num_seqs: int = 512,
              max_batched_tokens: int = 16384, device: int = 0, num_state_slots: int = 0):
@@ -460,6 +547,7 @@ class ListedModelConfig:
         c.max_num_seqs, c.max_batched_tokens, c.device = max_num_seqs, max_batched_tokens, device
         c.block_style, c.position, c.tied_head = self.block_style, self.position, int(self.tied_head)
         c.norm_offset, c.num_state_slots = self.norm_offset, num_state_slots
+        c.loop_start, c.loop_stop, c.loop_times = self.loop_start, self.loop_stop, self.loop_times
         specs = (CLayerSpec * len(self.layers))(*[l.to_c() for l in self.layers])
         return c, specs
 
@@ -530,8 +618,77 @@ def zozonex_from_json(j: dict) -> ListedModelConfig:
         tied_head=True, norm_offset=1.0)
 
 
+def _lazovik_layer(i: int, lc: dict, shapes: dict) -> LayerSpec:
+    m = lc["mixer"]
+    kind = lc.get("type")
+
+    def inner(name: str) -> int:
+        # the inner size of the decay's two-step projection is given by the tensor's shape only
+        if name not in shapes:
+            raise ValueError(f"layer {i}: the checkpoint has no tensor {name}")
+        return int(shapes[name][0])
+
+    if kind == "gla":
+        kw = dict(mixer=MIXER_GLA, heads=int(m["heads"]), dim=int(m["dim"]), vdim=int(m["vdim"]),
+                  tau=float(m["tau"]), lowrank=inner(f"l{i}.mix.a1"))
+    elif kind == "parallel":
+        a, b = m["left"], m["right"]
+        rot = a.get("rot") or {}
+        sc = rot.get("scaling") or {}
+        mask = a.get("mask") or {}
+        kw = dict(mixer=MIXER_ATTN_TMIX, heads=int(a["heads"]), kv_heads=int(a["kv_heads"]), dim=int(a["dim"]),
+                  vdim=int(a["vdim"]), conv=int(a.get("conv") or 1), scale=float(a["scale"]),
+                  softcap=float(a.get("softcap") or 0.0), chunk=int(mask.get("size") or 0), qk_norm=2,
+                  proj_bias=1, out_gate=1, rot_dims=int(rot.get("dims") or 0), rot_base=float(rot.get("base") or 0.0),
+                  rot_factor=float(sc.get("factor") or 0.0), rot_original=float(sc.get("original") or 0.0),
+                  rot_fast=float(sc.get("fast") or 0.0), rot_slow=float(sc.get("slow") or 0.0),
+                  heads2=int(b["heads"]), dim2=int(b["dim"]), lowrank=inner(f"l{i}.mix.right.w1"),
+                  mix_scale=float(m["left_scale"]), mix2_scale=float(m["right_scale"]))
+    else:
+        raise ValueError(f"layer {i}: unknown layer type {kind!r}")
+    mlp = lc.get("mlp")
+    if mlp is None:
+        pass
+    elif mlp["kind"] == "moe":
+        r = mlp["router"]
+        kw.update(mlp=MLP_MOE, act=FFN_RELU2, ff=int(mlp["expert"]["ff"]), experts=int(r["experts"]), top=int(r["top"]),
+                  route_sigmoid=1, weight_on_input=1, shared_ff=int((mlp.get("shared") or {}).get("ff") or 0))
+    else:
+        raise ValueError(f"layer {i}: unknown feed-forward kind {mlp['kind']!r}")
+    return LayerSpec(**kw)
+
+
+def lazovik_from_json(j: dict, shapes: Optional[dict] = None) -> ListedModelConfig:
+    """config.json of the Lazovik design: gated-linear-attention layers and layers that run a
+    convolved, gated, chunk-masked attention beside RWKV-style time mixing; pre-norm blocks, a
+    mixture of squared-ReLU experts with an always-on expert; a run of layers may repeat.
+    `shapes`: tensor name -> shape of the checkpoint (sizes that only a tensor's shape gives)."""
+    lp = j.get("loop") or {}
+    times = int(lp.get("times") or 1)
+    return ListedModelConfig(
+        name="lazovik", vocab_size=int(j["vocab"]), hidden=int(j["width"]),
+        layers=tuple(_lazovik_layer(i, lc, shapes or {}) for i, lc in enumerate(j["layers"])),
+        norm_eps=float(j["norm"]["eps"]), arch=ARCH_LAZOVIK, block_style=LBLOCK_SEQUENTIAL_PRENORM,
+        loop_start=int(lp.get("start") or 0) if times > 1 else 0,
+        loop_stop=int(lp.get("stop") or 0) if times > 1 else 0, loop_times=times)
+
+
+def safetensors_shapes(model_dir: str) -> dict:
+    """Tensor name -> shape from the header of model.safetensors (8-byte little-endian length,
+    then that many bytes of JSON)."""
+    path = os.path.join(model_dir, "model.safetensors")
+    if not os.path.exists(path):
+        return {}
+    with open(path, "rb") as f:
+        n = int.from_bytes(f.read(8), "little")
+        hdr = json.loads(f.read(n))
+    return {k: tuple(v["shape"]) for k, v in hdr.items() if k != "__metadata__"}
+
+
 # model registry: config.json "architecture" -> config builder
-ARCHITECTURES = {"Dugopel": dugopel_from_json, "Zozonex": zozonex_from_json}
+ARCHITECTURES = {"Dugopel": dugopel_from_json, "Zozonex": zozonex_from_json, "Lazovik": lazovik_from_json}
+# builders that also want the checkpoint's tensor shapes
+_WANTS_SHAPES = {"Lazovik"}
 
 
 def from_model_dir(model_dir: str):
@@ -541,4 +698,6 @@ def from_model_dir(model_dir: str):
     arch = j.get("architecture")
     if arch not in ARCHITECTURES:
         raise ValueError(f"config.json names architecture {arch!r}; known: {sorted(ARCHITECTURES)}")
+    if arch in _WANTS_SHAPES:
+        return ARCHITECTURES[arch](j, safetensors_shapes(model_dir))
     return ARCHITECTURES[arch](j)

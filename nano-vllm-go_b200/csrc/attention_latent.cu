@@ -35,7 +35,7 @@ constexpr int LAT_NACC = 16;    // accumulator registers per lane: R <= 32 * LAT
 // ---------------------------------------------------------------- rope table
 __global__ void rope_table_kernel(const int* __restrict__ positions, int T, int half,
                                   const double* __restrict__ inv_freq, float* __restrict__ cosT,
-                                  float* __restrict__ sinT) {
+                                  float* __restrict__ sinT, double mult) {
   pdl_launch_dependents();
   pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -43,15 +43,15 @@ __global__ void rope_table_kernel(const int* __restrict__ positions, int T, int 
   const int t = i / half, j = i % half;
   double s, c;
   sincos((double)positions[t] * inv_freq[j], &s, &c);
-  cosT[i] = (float)c;
-  sinT[i] = (float)s;
+  cosT[i] = (float)(c * mult);
+  sinT[i] = (float)(s * mult);
 }
 cudaError_t launch_rope_table(cudaStream_t st, const int* positions, int T, int half,
-                              const double* inv_freq, float* cosT, float* sinT) {
+                              const double* inv_freq, float* cosT, float* sinT, double mult) {
   if (T <= 0 || half <= 0) return cudaSuccess;
   const int n = T * half;
   (void)launch_k(rope_table_kernel, dim3((n + 255) / 256), dim3(256), 0, st, positions, T, half, inv_freq,
-                 cosT, sinT);
+                 cosT, sinT, mult);
   return cudaGetLastError();
 }
 

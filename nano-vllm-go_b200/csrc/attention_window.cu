@@ -6,6 +6,11 @@
 //   s_ij = scale * q_i . k_j   for 0 <= i - j < window (window = 0: every j <= i)
 //   p_ij = exp(s_ij) / (sink + sum_j exp(s_ij))                    sink = 1: a key of score 0 without a value
 //   o_i  = sum_j p_ij v_j;  query head h reads key / value head h / (H / G)
+// Options of the same kernels (WinAttnArgs): chunk > 0 replaces the window by a chunked mask — i sees
+// j <= i with i / chunk == j / chunk, chunks counted from position 0 of the sequence —, softcap > 0
+// caps the score, s <- softcap * tanh(s / softcap), before the mask, and gate multiplies the
+// normalised output element by element.  Both masks give every query a contiguous key range
+// [first_key(i), i] whose start does not decrease with i, which is all the tile logic relies on.
 //
 //  * winattn_prep_kernel: epilogue of the fused projection [Q | K | V] — split-K sum, the
 //    per-head norms, Q to the activation dtype, K / V rows into the layer's pools at slots[t]
@@ -31,6 +36,14 @@
 namespace nvllm {
 
 namespace {
+// first key position i sees
+__device__ __forceinline__ int first_key(const WinAttnArgs& a, int i) {
+  if (a.chunk > 0) return i / a.chunk * a.chunk;
+  return a.window > 0 ? max(0, i - a.window + 1) : 0;
+}
+// cap * tanh(s / cap), the library tanh: a score is small beside the cap more often than not, and
+// there a tanh built on a fast exponential loses the digits that fp32 scores are asked to keep
+__device__ __forceinline__ float cap_score(float s, float cap) { return cap * tanhf(s / cap); }
 __device__ __forceinline__ float sum_slices(const float* __restrict__ p, int S, size_t stride) {
   float acc = 0.f;
   for (int s = 0; s < S; s++) acc += p[(size_t)s * stride];
@@ -129,6 +142,103 @@ cudaError_t launch_winattn_prep(cudaStream_t st, int qdt, int kvdt, const WinAtt
   return cudaGetLastError();
 }
 
+// ------------------------------------------------------------------ projection epilogue with a short convolution
+// One CTA per token.  Pass 1: every q / k / v channel's convolution over the last `taps` projected
+// rows (this step's rows through the partials, earlier ones through the slot's tail), q and k
+// staged in shared memory with their sums of squares, v straight into the pool, the gates'
+// sigmoids out.  Pass 2: the two whole-row norms, weights, rotation, Q and K out.
+template <typename QT, typename KT>
+__global__ void __launch_bounds__(256) winattn_prep_conv_kernel(WinAttnArgs a, ConvAttnPrep c, Trace tr) {
+  TRACE_ENTRY(tr);
+  pdl_launch_dependents();
+  extern __shared__ float qk[];  // [n_q + n_k] convolved
+  __shared__ float red[32];
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int n_q = a.H * a.dim, n_k = a.G * a.dim, n_v = a.G * a.vdim, n_ch = n_q + n_k + n_v;
+  // sequence of the row: one row per sequence in a decode step, else a search through the offsets
+  int s = t;
+  if (a.T != a.n_seqs) {
+    int lo = 0, hi = a.n_seqs - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (a.cu_q[mid] <= t) lo = mid;
+      else hi = mid - 1;
+    }
+    s = lo;
+  }
+  const int r0 = a.cu_q[s];
+  const int li = t - r0, pos = c.positions[t];
+  const int keep = c.taps - 1;
+  const float* tail = c.state_pool + (size_t)c.state_slots[s] * c.slot_floats + c.tail_off;
+  const int slot = a.slots[t];
+  const int blk = slot / KV_BLOCK, off = slot % KV_BLOCK;
+  float ssq = 0.f, ssk = 0.f;
+  for (int ch = threadIdx.x; ch < n_ch; ch += blockDim.x) {
+    const float b = c.bias ? c.bias[ch] : 0.f;
+    float y = 0.f;
+    for (int j = 0; j < c.taps; j++) {
+      const int back = keep - j;  // input `back` positions before this token
+      float u = 0.f;
+      if (back <= li) u = sum_slices(a.in_p + (size_t)(t - back) * a.in_ld + ch, a.in_S, a.in_stride) + b;
+      else if (back <= pos) u = tail[(size_t)(keep - (back - li)) * n_ch + ch];
+      y = fmaf(c.conv_w[(size_t)ch * c.taps + j], u, y);
+    }
+    if (ch < n_q) { qk[ch] = y; ssq += y * y; }
+    else if (ch < n_q + n_k) { qk[ch] = y; ssk += y * y; }
+    else {
+      const int vc = ch - n_q - n_k, g = vc / a.vdim, i = vc % a.vdim;
+      ((KT*)a.vpool)[(((size_t)blk * a.G + g) * KV_BLOCK + off) * a.vdim + i] = from_f32<KT>(y);
+    }
+  }
+  if (c.gate_out) {
+    const int n_g = a.H * a.vdim;
+    for (int i = threadIdx.x; i < n_g; i += blockDim.x) {
+      const float z = sum_slices(a.in_p + (size_t)t * a.in_ld + n_ch + i, a.in_S, a.in_stride);
+      c.gate_out[(size_t)t * c.gate_ld + i] = 1.0f / (1.0f + expf(-z));
+    }
+  }
+  const float inv_q = 1.0f / sqrtf(block_sum(ssq, red) / (float)n_q + a.eps);
+  const float inv_k = 1.0f / sqrtf(block_sum(ssk, red) / (float)n_k + a.eps);
+  const float* cs = c.cosT + (size_t)t * c.rot_half;
+  const float* sn = c.sinT + (size_t)t * c.rot_half;
+  const int rot = 2 * c.rot_half;
+  for (int ch = threadIdx.x; ch < n_q + n_k; ch += blockDim.x) {
+    const bool isq = ch < n_q;
+    const int cc = isq ? ch : ch - n_q;
+    const int hh = cc / a.dim, i = cc % a.dim;
+    const float inv = isq ? inv_q : inv_k;
+    const float* w = isq ? c.qnorm_w : c.knorm_w;
+    float v = qk[ch] * inv * w[cc];
+    if (i < rot) {
+      const int ip = i < c.rot_half ? i + c.rot_half : i - c.rot_half;  // the entry it is paired with
+      const int pch = ch - i + ip;
+      const float o = qk[pch] * inv * w[cc - i + ip];
+      const int f = i < c.rot_half ? i : ip;
+      v = i < c.rot_half ? v * cs[f] - o * sn[f] : v * cs[f] + o * sn[f];
+    }
+    if (isq) ((QT*)a.q)[(size_t)t * n_q + cc] = from_f32<QT>(v);
+    else ((KT*)a.kpool)[(((size_t)blk * a.G + hh) * KV_BLOCK + off) * a.dim + i] = from_f32<KT>(v);
+  }
+  TRACE_EXIT(tr);
+}
+
+cudaError_t launch_winattn_prep_conv(cudaStream_t st, int qdt, int kvdt, const WinAttnArgs& a, const ConvAttnPrep& c) {
+  if (a.T <= 0) return cudaSuccess;
+  if (c.taps < 1 || 2 * c.rot_half > a.dim || !a.own_kv) return cudaErrorInvalidValue;
+  const size_t smem = (size_t)(a.H + a.G) * a.dim * sizeof(float);
+  if (qdt == DT_F32 && kvdt == DT_F32) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(winattn_prep_conv_kernel<float, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    (void)launch_k(winattn_prep_conv_kernel<float, float>, dim3(a.T), dim3(256), smem, st, a, c, next_trace(38));
+  } else if (qdt == DT_BF16 && kvdt == DT_BF16) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(winattn_prep_conv_kernel<bf16, bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    (void)launch_k(winattn_prep_conv_kernel<bf16, bf16>, dim3(a.T), dim3(256), smem, st, a, c, next_trace(38));
+  } else {
+    return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+
 // ------------------------------------------------------------------ attention, fp32 arithmetic
 constexpr int WA_KT = 32;  // keys per tile (divides KV_BLOCK)
 constexpr int WA_QS = 16;  // queries per sub-tile: 8 warps x 2
@@ -180,7 +290,7 @@ __global__ void __launch_bounds__(256) winattn_kernel(WinAttnArgs a, Trace tr) {
       for (int c = 0; c < VPL; c++) acc[qq][c] = 0.f;
     }
     const int p_first = qpos0 + qb, p_last = qpos0 + qb + nqs - 1;
-    int k_lo = a.window > 0 ? max(0, p_first - a.window + 1) : 0;
+    int k_lo = first_key(a, p_first);
     k_lo = k_lo / WA_KT * WA_KT;
     const int k_hi = p_last + 1;
     for (int k0 = k_lo; k0 < k_hi; k0 += WA_KT) {
@@ -200,14 +310,14 @@ __global__ void __launch_bounds__(256) winattn_kernel(WinAttnArgs a, Trace tr) {
         if (qi >= nqs) continue;  // warp-uniform
         const int qp = p_first + qi;
         const int j = k0 + lane;
-        const bool vis = lane < nk && j <= qp && (a.window <= 0 || qp - j < a.window);
+        const bool vis = lane < nk && j <= qp && j >= first_key(a, qp);
         float s = -INFINITY;
         if (vis) {
           const float* qr = Qs + qi * dim;
           const float* kr = Ks + lane * kld;
           float d = 0.f;
           for (int i = 0; i < dim; i++) d = fmaf(qr[i], kr[i], d);
-          s = d;
+          s = a.softcap > 0.f ? cap_score(d, a.softcap) : d;
         }
         const float cmax = warp_max(s);
         if (cmax == -INFINITY) continue;  // no key of this tile is visible to the query
@@ -236,10 +346,11 @@ __global__ void __launch_bounds__(256) winattn_kernel(WinAttnArgs a, Trace tr) {
       if (qi >= nqs) continue;
       const float inv = 1.0f / l[qq];
       QT* op = (QT*)a.out + (size_t)(row0 + qb + qi) * a.o_ld;
+      const float* gt = a.gate ? a.gate + (size_t)(row0 + qb + qi) * a.gate_ld + head * vdim : nullptr;
 #pragma unroll
       for (int c = 0; c < VPL; c++) {
         const int col = lane + 32 * c;
-        if (col < vdim) op[head * vdim + col] = from_f32<QT>(acc[qq][c] * inv);
+        if (col < vdim) op[head * vdim + col] = from_f32<QT>(acc[qq][c] * inv * (gt ? gt[col] : 1.f));
       }
       if (head == 0)  // padding columns of the output projection's input stay zero
         for (int col = a.H * vdim + lane; col < a.o_ld; col += 32) op[col] = from_f32<QT>(0.f);
@@ -288,7 +399,7 @@ __global__ void __launch_bounds__(128) winattn_decode_kernel(WinAttnArgs a, Trac
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = head / (a.H / a.G);
   const int qp = a.seq_len[seq] - 1;
-  const int k_lo = a.window > 0 ? max(0, qp - a.window + 1) : 0;
+  const int k_lo = first_key(a, qp);
   const int* bt = a.block_tables + (size_t)seq * a.max_blocks;
   const KT* kpool = (const KT*)a.kpool;
   const KT* vpool = (const KT*)a.vpool;
@@ -306,7 +417,7 @@ __global__ void __launch_bounds__(128) winattn_decode_kernel(WinAttnArgs a, Trac
       const KT* kr = kpool + (((size_t)bt[j / KV_BLOCK] * a.G + g) * KV_BLOCK + (j % KV_BLOCK)) * dim;
       float d = 0.f;
       for (int i = 0; i < dim; i++) d = fmaf(qs[i], to_f32(kr[i]), d);
-      s = d;
+      s = a.softcap > 0.f ? cap_score(d, a.softcap) : d;
     }
     const float mn = fmaxf(m, warp_max(s));  // lane 0 of the chunk is always visible
     const float corr = (m == -INFINITY) ? 0.f : expf(m - mn);
@@ -351,6 +462,7 @@ __global__ void __launch_bounds__(128) winattn_decode_kernel(WinAttnArgs a, Trac
   for (int col = threadIdx.x; col < vdim; col += blockDim.x) {
     float v = 0.f;
     for (int w = 0; w < 4; w++) v += part[w * (vdim + 2) + col] * cw[w];
+    if (a.gate) v *= a.gate[(size_t)seq * a.gate_ld + head * vdim + col];
     op[head * vdim + col] = from_f32<QT>(v / lt);
   }
   if (head == 0)
@@ -405,7 +517,7 @@ __global__ void __launch_bounds__(256, (GQMAX * VPT <= 16) ? 2 : 1) winattn_deco
   float* part = smem + GQMAX * dim;            // [WD_WARPS][GQMAX][vdim + 2]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int qp = a.seq_len[seq] - 1;
-  const int k_lo = a.window > 0 ? max(0, qp - a.window + 1) : 0;
+  const int k_lo = first_key(a, qp);
   const int* bt = a.block_tables + (size_t)seq * a.max_blocks;
   const KT* kpool = (const KT*)a.kpool;
   const KT* vpool = (const KT*)a.vpool;
@@ -456,7 +568,7 @@ __global__ void __launch_bounds__(256, (GQMAX * VPT <= 16) ? 2 : 1) winattn_deco
     float p[GQMAX];
 #pragma unroll
     for (int q = 0; q < GQMAX; q++) {
-      const float sv = vis ? s[q] : -INFINITY;
+      const float sv = vis ? (a.softcap > 0.f ? cap_score(s[q], a.softcap) : s[q]) : -INFINITY;
       const float mn = fmaxf(m[q], warp_max(sv));  // lane 0 of a chunk is always visible
       const float corr = (m[q] == -INFINITY) ? 0.f : expf(m[q] - mn);
       p[q] = vis ? expf(sv - mn) : 0.f;
@@ -510,6 +622,7 @@ __global__ void __launch_bounds__(256, (GQMAX * VPT <= 16) ? 2 : 1) winattn_deco
       lt += pw[vdim + 1] * cw;
       v += pw[col] * cw;
     }
+    if (a.gate) v *= a.gate[(size_t)seq * a.gate_ld + (size_t)(h0 + q) * vdim + col];
     ((QT*)a.out)[(size_t)seq * a.o_ld + (size_t)(h0 + q) * vdim + col] = from_f32<QT>(v / lt);
   }
   if (g == 0 && blockIdx.z == 0)
@@ -614,7 +727,7 @@ __global__ void __launch_bounds__(128) winattn_mma_kernel(WinAttnArgs a, Trace t
     const bool ok = r < nq;
     cp_async16(smem_addr(Qs + r * DP + c * 8), ok ? (const void*)(qg + (size_t)r * a.H * DIM + c * 8) : (const void*)qg, ok);
   }
-  int k_lo = a.window > 0 ? max(0, qpos0 - a.window + 1) : 0;
+  int k_lo = first_key(a, qpos0);
   k_lo = k_lo / WM_K * WM_K;
   const int k_hi = qpos0 + nq;  // keys [k_lo, k_hi)
   const int n_kt = (k_hi - k_lo + WM_K - 1) / WM_K;
@@ -661,7 +774,7 @@ __global__ void __launch_bounds__(128) winattn_mma_kernel(WinAttnArgs a, Trace t
     const bf16* vd = Vs + buf * WM_K * VP;
     // does any row of this warp see any key of the tile?
     const int w_qlo = qpos0 + warp * 16, w_qhi = w_qlo + 15;
-    const bool warp_sees = warp * 16 < nq && k0 <= w_qhi && (a.window <= 0 || k0 + WM_K - 1 > w_qlo - a.window);
+    const bool warp_sees = warp * 16 < nq && k0 <= w_qhi && k0 + WM_K - 1 >= first_key(a, w_qlo);
     if (warp_sees) {
       float s[WM_K / 8][4];
 #pragma unroll
@@ -684,8 +797,14 @@ __global__ void __launch_bounds__(128) winattn_mma_kernel(WinAttnArgs a, Trace t
       }
       // scale (scores live in the base-2 domain: exp2 of a difference is one instruction), mask
       // (only on tiles that some row of the warp sees partly), running max
-      const bool interior = k0 + WM_K - 1 <= w_qlo && k0 + WM_K <= k_hi && (a.window <= 0 || w_qhi - k0 < a.window);
+      const bool interior = k0 + WM_K - 1 <= w_qlo && k0 + WM_K <= k_hi && k0 >= first_key(a, w_qhi);
       float mx_lo = -INFINITY, mx_hi = -INFINITY;
+      if (a.softcap > 0.f) {  // the cap works on the scaled score; back to the base-2 domain afterwards
+#pragma unroll
+        for (int nb = 0; nb < WM_K / 8; nb++)
+#pragma unroll
+          for (int e = 0; e < 4; e++) s[nb][e] = cap_score(s[nb][e] * a.scale, a.softcap) * (1.4426950408889634f / sc);
+      }
       if (interior) {
 #pragma unroll
         for (int nb = 0; nb < WM_K / 8; nb++) {
@@ -700,7 +819,7 @@ __global__ void __launch_bounds__(128) winattn_mma_kernel(WinAttnArgs a, Trace t
           for (int e = 0; e < 4; e++) {
             const int j = k0 + nb * 8 + tig * 2 + (e & 1);
             const int qp = (e & 2) ? qp_hi : qp_lo;
-            const bool vis = j <= qp && j < k_hi && (a.window <= 0 || qp - j < a.window);
+            const bool vis = j <= qp && j < k_hi && j >= first_key(a, qp);
             const float v = vis ? s[nb][e] * sc : -INFINITY;
             s[nb][e] = v;
             if (e & 2) mx_hi = fmaxf(mx_hi, v);
@@ -760,11 +879,17 @@ __global__ void __launch_bounds__(128) winattn_mma_kernel(WinAttnArgs a, Trace t
   cp_async_wait<0>();
   const float i_lo = 1.0f / l_lo, i_hi = 1.0f / l_hi;
   bf16* ob = (bf16*)a.out + (size_t)row0 * a.o_ld + head * VDIM;
+  const float* gb = a.gate ? a.gate + (size_t)row0 * a.gate_ld + head * VDIM : nullptr;
 #pragma unroll
   for (int i = 0; i < VDIM / 8; i++) {
     const int col = i * 8 + tig * 2;
-    if (r_lo < nq) *reinterpret_cast<uint32_t*>(ob + (size_t)r_lo * a.o_ld + col) = pack_bf16(o[i][0] * i_lo, o[i][1] * i_lo);
-    if (r_hi < nq) *reinterpret_cast<uint32_t*>(ob + (size_t)r_hi * a.o_ld + col) = pack_bf16(o[i][2] * i_hi, o[i][3] * i_hi);
+    float g0 = 1.f, g1 = 1.f, g2 = 1.f, g3 = 1.f;
+    if (gb) {
+      if (r_lo < nq) { g0 = gb[(size_t)r_lo * a.gate_ld + col]; g1 = gb[(size_t)r_lo * a.gate_ld + col + 1]; }
+      if (r_hi < nq) { g2 = gb[(size_t)r_hi * a.gate_ld + col]; g3 = gb[(size_t)r_hi * a.gate_ld + col + 1]; }
+    }
+    if (r_lo < nq) *reinterpret_cast<uint32_t*>(ob + (size_t)r_lo * a.o_ld + col) = pack_bf16(o[i][0] * i_lo * g0, o[i][1] * i_lo * g1);
+    if (r_hi < nq) *reinterpret_cast<uint32_t*>(ob + (size_t)r_hi * a.o_ld + col) = pack_bf16(o[i][2] * i_hi * g2, o[i][3] * i_hi * g3);
   }
   if (head == 0) {
     bf16* orow = (bf16*)a.out + (size_t)row0 * a.o_ld;
@@ -798,7 +923,7 @@ __global__ void __launch_bounds__(128) winattn_decode_mma_kernel(WinAttnArgs a, 
   const int GQ = a.H / a.G, h0 = g * GQ;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int qp = a.seq_len[seq] - 1;
-  const int k_lo = a.window > 0 ? max(0, qp - a.window + 1) : 0;
+  const int k_lo = first_key(a, qp);
   const int t_lo = k_lo / WM_K * WM_K;
   const int n_kt = (qp + 1 - t_lo + WM_K - 1) / WM_K;
   const int* bt = a.block_tables + (size_t)seq * a.max_blocks;
@@ -873,7 +998,8 @@ __global__ void __launch_bounds__(128) winattn_decode_mma_kernel(WinAttnArgs a, 
 #pragma unroll
         for (int e = 0; e < 4; e++) {
           const int j = j0 + nb * 8 + tig * 2 + (e & 1);
-          const float v = (j >= k_lo && j <= qp) ? s[nb][e] * sc : -INFINITY;  // every row sits at position qp
+          const float sv = a.softcap > 0.f ? cap_score(s[nb][e] * a.scale, a.softcap) * 1.4426950408889634f : s[nb][e] * sc;
+          const float v = (j >= k_lo && j <= qp) ? sv : -INFINITY;  // every row sits at position qp
           s[nb][e] = v;
           if (e & 2) mx_hi = fmaxf(mx_hi, v);
           else mx_lo = fmaxf(mx_lo, v);
@@ -950,6 +1076,7 @@ __global__ void __launch_bounds__(128) winattn_decode_mma_kernel(WinAttnArgs a, 
       lt += pw[VDIM + 1] * cw;
       v += pw[col] * cw;
     }
+    if (a.gate) v *= a.gate[(size_t)seq * a.gate_ld + (size_t)(h0 + r) * VDIM + col];
     ((bf16*)a.out)[(size_t)seq * a.o_ld + (size_t)(h0 + r) * VDIM + col] = __float2bfloat16_rn(v / lt);
   }
   if (g == 0)

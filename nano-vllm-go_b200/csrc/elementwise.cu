@@ -150,7 +150,7 @@ __global__ void __launch_bounds__(512) norm_kernel(NormArgs a, Trace tr) {
     if (threadIdx.x == 0 && trace_on(tr)) trace_rec(tr, t_entry, t_wait, 0ull);
     return;
   }
-  const bool upd = (a.p1 != nullptr) || (a.p2 != nullptr);
+  const bool upd = (a.p1 != nullptr) || (a.p2 != nullptr) || (a.xadd != nullptr);
   const bool ln = a.b != nullptr || a.centered != 0;  // LayerNorm (with or without the additive term)
   float lsum = 0.f;
   for (int i = i0; i < H; i += blockDim.x * 8) {
@@ -216,8 +216,15 @@ __global__ void __launch_bounds__(512) norm_kernel(NormArgs a, Trace tr) {
 #pragma unroll
         for (int j = 0; j < 8; j++) acc[j] += p[j];
       }
+      const float m2 = a.row_m2 ? a.m2 * a.row_m2[r] : a.m2;
 #pragma unroll
-      for (int j = 0; j < 8; j++) v[j] = v[j] + a.m2 * acc[j];
+      for (int j = 0; j < 8; j++) v[j] = v[j] + m2 * acc[j];
+    }
+    if (a.xadd) {
+      float p[8];
+      load8(a.xadd + i, p);
+#pragma unroll
+      for (int j = 0; j < 8; j++) v[j] += p[j];
     }
     if (upd) store8(xr + i, v);
     store8(row + i, v);
@@ -277,7 +284,18 @@ __global__ void __launch_bounds__(512) norm_kernel(NormArgs a, Trace tr) {
     }
     store8(yr + i, o);
     if (a.y_f32) store8(a.y_f32 + (size_t)orow * H + i, o);
-    if (a.router) store8(row + i, o);  // each thread overwrites only what it alone reads
+    if (a.router || a.gate_w) store8(row + i, o);  // each thread overwrites only what it alone reads
+  }
+  if (a.gate_w) {  // one number per token: sigmoid(normed row . gate_w), fp32
+    float d = 0.f;
+    for (int i = i0; i < H; i += blockDim.x * 8) {
+      float g[8];
+      load8(a.gate_w + i, g);
+#pragma unroll
+      for (int j = 0; j < 8; j++) d = fmaf(row[i + j], g[j], d);
+    }
+    d = block_sum(d, red);
+    if (threadIdx.x == 0) a.gate_out[orow] = 1.0f / (1.0f + expf(-d));
   }
   if (a.router) {
     __shared__ float probs[MOE_MAX_E];

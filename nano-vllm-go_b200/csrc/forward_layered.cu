@@ -10,6 +10,14 @@
 //     this style: sliding-window attention (attention_window.cu) and the gated delta rule
 //     (delta.cu); feed-forward W_down relu(W_up x)^2.  Positions enter once, as sinusoids
 //     added to the scaled embedding; the head may be the embedding table itself.
+//   sequential, pre-norm:    x += mixer(RMSNorm(x));  x += feed_forward(RMSNorm(x)); a run of layers
+//     may repeat with the same weights, every pass with caches and state of its own and a learned
+//     vector added to x at its start.  Mixers of this style: gated linear attention (linrec.cu) and
+//     "attention + time mixing" — grouped-query attention whose q / k / v pass a short convolution
+//     (attention_window.cu: whole-row norms, interpolated rotation, score cap, chunked mask, output
+//     gate) beside time mixing with a token shift (linrec.cu), their outputs summed with two scales.
+//     Feed-forward: a mixture of squared-ReLU experts chosen by sigmoid scores, the weight on the
+//     expert's input, plus an always-on expert with a per-token gate.
 // Mixer "latent attention" (attention_latent.cu): one fused input projection [W_dq | W_dkv | W_g]
 // of h, RMS-normed latents, the query up projection with W_uk folded in, the absorbed-query
 // attention over the paged latent cache (per-head sigmoid gate applied to its result), the output
@@ -38,7 +46,12 @@ void layered_free(nvllm_handle* h) {
     F(y.norm_w); F(y.w_in); F(y.dq_norm); F(y.dkv_norm); F(y.w_uq); F(y.w_uk); F(y.w_uv); F(y.w_o); F(y.w_q); F(y.w_ov);
     F(y.w1); F(y.w2); F(y.router); F(y.moe_in); F(y.moe_out);
     F(y.post1_w); F(y.post2_w); F(y.conv_w); F(y.a_log); F(y.dt_bias); F(y.onorm_w);
+    F(y.bias_in); F(y.o_bias); F(y.qnorm_w); F(y.knorm_w); F(y.lr_w2); F(y.lr_b); F(y.mu); F(y.bonus);
+    F(y.w_in2); F(y.w_o2); F(y.sh_gate);
   }
+  h->runs.clear();
+  F(h->loop_step);
+  h->loop_step = nullptr;
   h->ll.clear();
   for (void* p : h->lat_pools) F(p);
   h->lat_pools.clear();
@@ -105,7 +118,76 @@ int layered_set_weight(nvllm_handle* h, const char* cname, int dtype, const void
   if (name == "embed") mat(h->wte, h->V, W, W);
   else if (name == "head" && h->lm_head_owned) mat(h->lm_head, h->V, W, W);
   else if (name == "final.norm") { vec(h->lnf_w, W); d.add = noff; }
-  else if (parse_layer_name(name, &l, &rest) && l < h->L && h->ll[l].s.mixer != NVLLM_MIXER_LATENT_ATTENTION) {
+  else if (name == "loop.step" && h->loop_step) {
+    mat(h->loop_step, h->loop_times, W, W);
+    d.ddt = DT_F32; d.p = h->loop_step;
+  } else if (parse_layer_name(name, &l, &rest) && l < h->L &&
+             (h->ll[l].s.mixer == NVLLM_MIXER_GLA || h->ll[l].s.mixer == NVLLM_MIXER_ATTN_TMIX)) {
+    // sequential pre-norm blocks: gated linear attention / attention + time mixing, mixture of experts
+    ListedLayer& y = h->ll[l];
+    const nvllm_layer_spec& s = y.s;
+    auto f32mat = [&](float* p, int64_t rows, int64_t cols) { mat(p, rows, cols, (int)cols); d.ddt = DT_F32; d.p = p; };
+    if (rest == "norm1") vec(y.post1_w, W);
+    else if (rest == "norm2" && s.mlp != NVLLM_MLP_NONE) vec(y.post2_w, W);
+    else if (s.mixer == NVLLM_MIXER_GLA) {
+      const int hd = s.heads * s.dim, hv = s.heads * s.vdim;
+      if (rest == "mix.q") mat(y.w_in, hd, W, W, 0);
+      else if (rest == "mix.k") mat(y.w_in, hd, W, W, hd);
+      else if (rest == "mix.v") mat(y.w_in, hv, W, W, 2 * hd);
+      else if (rest == "mix.g") mat(y.w_in, hv, W, W, 2 * hd + hv);
+      else if (rest == "mix.a1") mat(y.w_in, s.lowrank, W, W, 2 * hd + 2 * hv);
+      else if (rest == "mix.a2") f32mat(y.lr_w2, hd, s.lowrank);
+      else if (rest == "mix.a2.b") vec(y.lr_b, hd);
+      else if (rest == "mix.norm") vec(y.onorm_w, s.vdim);
+      else if (rest == "mix.o") mat(y.w_o, W, hv, y.ov_p);
+    } else {
+      const int hv = s.heads * s.vdim, hd2 = s.heads2 * s.dim2, nch = y.n_q + y.n_k + y.n_v;
+      if (rest == "mix.left.q") mat(y.w_in, y.n_q, W, W, 0);
+      else if (rest == "mix.left.k") mat(y.w_in, y.n_k, W, W, y.n_q);
+      else if (rest == "mix.left.v") mat(y.w_in, y.n_v, W, W, y.n_q + y.n_k);
+      else if (rest == "mix.left.g" && s.out_gate) mat(y.w_in, hv, W, W, nch);
+      else if (rest == "mix.left.q.b" && s.proj_bias) vec(y.bias_in, y.n_q);
+      else if (rest == "mix.left.k.b" && s.proj_bias) vec(y.bias_in + y.n_q, y.n_k);
+      else if (rest == "mix.left.v.b" && s.proj_bias) vec(y.bias_in + y.n_q + y.n_k, y.n_v);
+      else if (rest == "mix.left.o.b" && s.proj_bias) vec(y.o_bias, W);
+      else if (rest == "mix.left.q.norm") vec(y.qnorm_w, y.n_q);
+      else if (rest == "mix.left.k.norm") vec(y.knorm_w, y.n_k);
+      else if (rest == "mix.left.q.conv") f32mat(y.conv_w, y.n_q, s.conv);
+      else if (rest == "mix.left.k.conv") f32mat(y.conv_w + (size_t)y.n_q * s.conv, y.n_k, s.conv);
+      else if (rest == "mix.left.v.conv") f32mat(y.conv_w + (size_t)(y.n_q + y.n_k) * s.conv, y.n_v, s.conv);
+      else if (rest == "mix.left.o") mat(y.w_o, W, hv, y.ov_p);
+      else if (rest == "mix.right.r") mat(y.w_in2, hd2, W, W, y.seg2[0]);
+      else if (rest == "mix.right.k") mat(y.w_in2, hd2, W, W, y.seg2[1]);
+      else if (rest == "mix.right.v") mat(y.w_in2, hd2, W, W, y.seg2[2]);
+      else if (rest == "mix.right.g") mat(y.w_in2, hd2, W, W, y.seg2[3]);
+      else if (rest == "mix.right.w1") mat(y.w_in2, s.lowrank, W, W, y.seg2[4]);
+      else if (rest == "mix.right.w2") f32mat(y.lr_w2, hd2, s.lowrank);
+      else if (rest == "mix.right.w0") vec(y.lr_b, hd2);
+      else if (rest == "mix.right.u") f32mat(y.bonus, s.heads2, s.dim2);
+      else if (rest == "mix.right.norm") vec(y.onorm_w, hd2);
+      else if (rest == "mix.right.o") mat(y.w_o2, W, hd2, y.ov2_p);
+      else if (rest.compare(0, 13, "mix.right.mu.") == 0 && rest.size() == 14) {
+        const char* order = "rkvgw";
+        const char* at = strchr(order, rest[13]);
+        if (at) vec(y.mu + (size_t)(at - order) * W, W);
+      }
+    }
+    if (!d.p && s.mlp == NVLLM_MLP_MOE) {
+      if (rest == "mlp.router") f32mat(y.router, s.experts, W);
+      else if (rest == "mlp.shared.up" && s.shared_ff > 0) mat(y.w1, s.shared_ff, W, W);
+      else if (rest == "mlp.shared.down" && s.shared_ff > 0) mat(y.w2, W, s.shared_ff, y.sff_p);
+      else if (rest == "mlp.shared.sg" && s.shared_ff > 0) f32mat(y.sh_gate, 1, W);
+      else if (rest.compare(0, 5, "mlp.e") == 0) {
+        size_t i = 5;
+        int e = 0;
+        while (i < rest.size() && rest[i] >= '0' && rest[i] <= '9') e = e * 10 + (rest[i++] - '0');
+        const std::string part = i < rest.size() ? rest.substr(i) : "";
+        if (i == 5 || e >= s.experts) return set_err(h, NVLLM_ERR_INVALID, "unknown tensor %s", cname);
+        if (part == ".up") mat(y.moe_in, s.ff, W, W, (size_t)e * y.ff_p);
+        else if (part == ".down") mat(y.moe_out, W, s.ff, y.ff_p, (size_t)e * W);
+      }
+    }
+  } else if (parse_layer_name(name, &l, &rest) && l < h->L && h->ll[l].s.mixer != NVLLM_MIXER_LATENT_ATTENTION) {
     // sequential post-norm blocks: window attention / delta rule mixers, relu^2 feed-forward
     ListedLayer& y = h->ll[l];
     const nvllm_layer_spec& s = y.s;
@@ -196,9 +278,36 @@ int layered_finalize(nvllm_handle* h) {
   };
   std::vector<std::string> need = {"embed", "final.norm"};
   if (h->lm_head_owned) need.push_back("head");
+  if (h->loop_step) need.push_back("loop.step");
   for (int l = 0; l < h->L; l++) {
     const nvllm_layer_spec& s = h->ll[l].s;
     const std::string p = "l" + std::to_string(l) + ".";
+    if (s.mixer == NVLLM_MIXER_GLA || s.mixer == NVLLM_MIXER_ATTN_TMIX) {
+      need.push_back(p + "norm1");
+      if (s.mixer == NVLLM_MIXER_GLA) {
+        for (const char* n : {"mix.q", "mix.k", "mix.v", "mix.g", "mix.a1", "mix.a2", "mix.a2.b", "mix.norm", "mix.o"})
+          need.push_back(p + n);
+      } else {
+        for (const char* n : {"mix.left.q", "mix.left.k", "mix.left.v", "mix.left.q.norm", "mix.left.k.norm",
+                              "mix.left.q.conv", "mix.left.k.conv", "mix.left.v.conv", "mix.left.o", "mix.right.r",
+                              "mix.right.k", "mix.right.v", "mix.right.g", "mix.right.w1", "mix.right.w2", "mix.right.w0",
+                              "mix.right.u", "mix.right.norm", "mix.right.o", "mix.right.mu.r", "mix.right.mu.k",
+                              "mix.right.mu.v", "mix.right.mu.g", "mix.right.mu.w"})
+          need.push_back(p + n);
+        if (s.out_gate) need.push_back(p + "mix.left.g");
+        if (s.proj_bias)
+          for (const char* n : {"mix.left.q.b", "mix.left.k.b", "mix.left.v.b", "mix.left.o.b"}) need.push_back(p + n);
+      }
+      if (s.mlp == NVLLM_MLP_MOE) {
+        need.push_back(p + "norm2");
+        need.push_back(p + "mlp.router");
+        for (int e = 0; e < s.experts; e++)
+          for (const char* n : {".up", ".down"}) need.push_back(p + "mlp.e" + std::to_string(e) + n);
+        if (s.shared_ff > 0)
+          for (const char* n : {"mlp.shared.up", "mlp.shared.down", "mlp.shared.sg"}) need.push_back(p + n);
+      }
+      continue;
+    }
     if (s.mixer != NVLLM_MIXER_LATENT_ATTENTION) {
       for (const char* n : {"norm1", "mix.q", "mix.o"}) need.push_back(p + n);
       if (s.mixer == NVLLM_MIXER_DELTA) {
@@ -250,8 +359,23 @@ int layered_finalize(nvllm_handle* h) {
   }
   // cache pools: one per layer with its own down projection, rows [c | rotated key part]
   h->lat_pools.assign(h->L, nullptr);
-  h->win_kpools.assign(h->L, nullptr);
-  h->win_vpools.assign(h->L, nullptr);
+  // (pre-norm blocks: one K / V pool per EXECUTION of an attention layer, see LayerRun)
+  const size_t n_pools = std::max((size_t)h->L, h->runs.size());
+  h->win_kpools.assign(n_pools, nullptr);
+  h->win_vpools.assign(n_pools, nullptr);
+  for (size_t r = 0; r < h->runs.size(); r++) {
+    const ListedLayer& y = h->ll[h->runs[r].layer];
+    if (y.s.mixer != NVLLM_MIXER_ATTN_TMIX) continue;
+    const size_t rows = (size_t)h->num_blocks * y.s.kv_heads * KV_BLOCK;
+    const size_t kb = rows * y.s.dim * dt_size(h->kvdt), vb = rows * y.s.vdim * dt_size(h->kvdt);
+    cudaError_t e = cudaMalloc(&h->win_kpools[r], kb);
+    if (e == cudaSuccess) e = cudaMalloc(&h->win_vpools[r], vb);
+    if (e != cudaSuccess)
+      return set_err(h, NVLLM_ERR_NOMEM, "K / V cache of %d blocks does not fit: %s", h->num_blocks, cudaGetErrorString(e));
+    NV_CHECK(h, cudaMemsetAsync(h->win_kpools[r], 0, kb, h->stream));
+    NV_CHECK(h, cudaMemsetAsync(h->win_vpools[r], 0, vb, h->stream));
+    h->kv_bytes += kb + vb;
+  }
   for (int l = 0; l < h->L; l++) {
     ListedLayer& y = h->ll[l];
     if (y.s.mixer != NVLLM_MIXER_WINDOW_ATTENTION || y.s.kv_from >= 0) continue;
@@ -297,6 +421,16 @@ int layered_finalize(nvllm_handle* h) {
     const int half = r.dims / 2;
     std::vector<double> f(half);
     for (int i = 0; i < half; i++) f[i] = pow(r.base, -2.0 * (double)i / (double)r.dims);
+    if (r.factor > 0) {
+      // entry at which a wavelength of original / turns is reached
+      auto at = [&](double turns) { return r.dims * log(r.original / (2.0 * M_PI * turns)) / (2.0 * log(r.base)); };
+      const double lo = std::max(floor(at(r.fast)), 0.0), hi = std::min(ceil(at(r.slow)), (double)r.dims - 1.0);
+      for (int i = 0; i < half; i++) {
+        const double ramp = std::min(std::max(((double)i - lo) / std::max(hi - lo, 0.001), 0.0), 1.0);
+        f[i] = f[i] / r.factor * ramp + f[i] * (1.0 - ramp);
+      }
+      r.mult = 0.1 * log(r.factor) + 1.0;
+    }
     NV_CHECK(h, cudaMalloc((void**)&r.inv_freq, (size_t)half * 8));
     NV_CHECK(h, cudaMemcpy(r.inv_freq, f.data(), (size_t)half * 8, cudaMemcpyHostToDevice));
   }
@@ -450,6 +584,257 @@ static int forward_layers_postnorm(nvllm_handle* h) {
   return NVLLM_OK;
 }
 
+// ------------------------------------------------------------------ sequential pre-norm blocks
+static LinSeg seg_of(const Pending& p, int ld, int col) {
+  LinSeg g;
+  g.p = p.p + col; g.S = p.S; g.stride = p.stride; g.ld = ld;
+  return g;
+}
+
+// x += pending sublayer results (+ the vector that opens a pass); xn = RMSNorm(x) * w.  With `moe`
+// the kernel also routes the normed row and computes the always-on expert's gate.
+static int run_prenorm(nvllm_handle* h, Pending* p1, Pending* p2, const float* row_m2, const float* xadd, const float* w,
+                       const ListedLayer* moe, int T) {
+  Workspace& ws = h->ws;
+  NormArgs a{};
+  a.x = ws.x;
+  double bytes = (double)T * h->H * (4 + dt_size(h->adt)), impl = 0.0;
+  if (p1->p) {
+    a.p1 = p1->p; a.S1 = p1->S; a.stride1 = p1->stride; a.m1 = p1->m; a.bias1 = p1->bias;
+    a.comb_rows = p1->comb_rows; a.comb_w = p1->comb_w; a.comb_k = p1->comb_k;
+    bytes += (double)T * h->H * 8;
+    impl += (double)T * h->H * 4 * ((p1->comb_rows ? p1->comb_k : p1->S) - 1);
+  }
+  if (p2->p) {
+    a.p2 = p2->p; a.S2 = p2->S; a.stride2 = p2->stride; a.m2 = p2->m; a.bias2 = p2->bias;
+    a.row_m2 = row_m2;
+    bytes += (double)T * h->H * 4;
+    impl += (double)T * h->H * 4 * (p2->S - 1);
+  }
+  a.xadd = xadd;
+  a.w = w; a.eps = h->cfg.norm_eps; a.y = ws.xn; a.ydt = h->adt;
+  a.n_rows = T; a.H = h->H;
+  if (moe) {
+    const nvllm_layer_spec& s = moe->s;
+    a.router = moe->router; a.E = s.experts; a.topk = s.top;
+    a.topk_idx = ws.topk_idx; a.topk_w = ws.topk_w;
+    a.route = RouteOpts{0, 0, 1, 1.f, s.route_sigmoid, s.weight_on_input};
+    if (s.shared_ff > 0) { a.gate_w = moe->sh_gate; a.gate_out = ws.sh_gate; }
+    bytes += (double)s.experts * h->H * 4;
+  }
+  ProfScope ps(h, NVLLM_K_NORM, bytes, 0, impl);
+  LAUNCH(h, launch_norm(h->stream, a));
+  *p1 = Pending();
+  *p2 = Pending();
+  return NVLLM_OK;
+}
+
+static void linrec_common(nvllm_handle* h, LinRecArgs* a, const LayerRun& r) {
+  const StepLayout& L = h->lay;
+  const int32_t* d = L.d;
+  a->T = L.T; a->n_seqs = L.n;
+  a->eps = h->cfg.norm_eps;
+  a->cu_q = d + L.cu_q; a->positions = d + L.positions; a->state_slots = d + L.state_slots;
+  a->state_pool = h->state_pool; a->slot_floats = h->state_slot_floats; a->state_off = r.state_off;
+  a->qkw = h->ws.lr_qkw; a->vv = h->ws.lr_v; a->o = h->ws.lr_o;
+  a->out = h->ws.attn_out;
+}
+// prep, scan and gated norm of a linear recurrence; the caller has filled the segments
+static int run_linrec(nvllm_handle* h, const LinRecArgs& a, double in_cols, int in_S) {
+  const int T = a.T;
+  const double hd = (double)a.H * a.dim, hv = (double)a.H * a.vdim, asz = dt_size(h->adt);
+  {
+    ProfScope ps(h, NVLLM_K_RECUR, (double)T * (in_cols * 4 + (3 * hd + hv) * 4) + hd * a.rank * 4, 2.0 * T * hd * a.rank,
+                 (double)T * in_cols * 4 * (in_S - 1));
+    LAUNCH(h, launch_linrec_prep(h->stream, a));
+  }
+  {
+    // algorithmic: every sequence's state once in and once out, the token inputs once, the read-outs once
+    const double state = (double)a.n_seqs * hd * a.vdim * 4 * 2;
+    ProfScope ps(h, NVLLM_K_RECUR, state + (double)T * (3 * hd + 2 * hv) * 4, 4.0 * T * hv * a.dim);
+    LAUNCH(h, launch_linrec_scan(h->stream, a));
+  }
+  {
+    ProfScope ps(h, NVLLM_K_RECUR, (double)T * hv * (4 + 4 + asz), 0, (double)T * hv * 4 * (a.gate.S - 1));
+    LAUNCH(h, launch_linrec_out(h->stream, h->adt, a));
+  }
+  return NVLLM_OK;
+}
+
+static int mixer_gla(nvllm_handle* h, const ListedLayer& y, const LayerRun& r, Pending* out) {
+  Workspace& w = h->ws;
+  const nvllm_layer_spec& s = y.s;
+  const int T = h->lay.T, H = h->H;
+  const int hd = s.heads * s.dim, hv = s.heads * s.vdim;
+  int rc;
+  Pending pin;
+  if ((rc = run_gemm(h, w.xn, H, y.w_in, T, y.n_in, H, 1.f, w.ws_a, w.ws_a_floats, y.n_in, &pin))) return rc;
+  LinRecArgs a{};
+  linrec_common(h, &a, r);
+  a.H = s.heads; a.dim = s.dim; a.vdim = s.vdim; a.tmix = 0;
+  a.tau = s.tau; a.qmul = 1.0f / sqrtf((float)s.dim);
+  a.q = seg_of(pin, y.n_in, 0); a.k = seg_of(pin, y.n_in, hd); a.v = seg_of(pin, y.n_in, 2 * hd);
+  a.gate = seg_of(pin, y.n_in, 2 * hd + hv); a.lr = seg_of(pin, y.n_in, 2 * hd + 2 * hv);
+  a.rank = s.lowrank; a.w2 = y.lr_w2; a.w2b = y.lr_b;
+  a.onorm_w = y.onorm_w; a.onorm_ld = 0;
+  a.o_ld = y.ov_p;
+  if ((rc = run_linrec(h, a, y.n_in, pin.S))) return rc;
+  return run_gemm(h, w.attn_out, y.ov_p, y.w_o, T, H, y.ov_p, 1.f, w.ws_b, w.ws_b_floats, H, out);
+}
+
+// Two mixers on the same normed input: *pa = attention (its scale and output bias ride in the
+// pending addend), *pb = time mixing.
+static int mixer_attn_tmix(nvllm_handle* h, const ListedLayer& y, const LayerRun& r, int run_idx, Pending* pa, Pending* pb) {
+  const StepLayout& L = h->lay;
+  Workspace& w = h->ws;
+  const nvllm_layer_spec& s = y.s;
+  const int T = L.T, H = h->H;
+  const int32_t* d = L.d;
+  const double asz = dt_size(h->adt), kvsz = dt_size(h->kvdt);
+  const size_t wsz = dt_size(h->wdt);
+  int rc;
+  // ---- attention side
+  Pending pin;
+  if ((rc = run_gemm(h, w.xn, H, y.w_in, T, y.n_in, H, 1.f, w.ws_a, w.ws_a_floats, y.n_in, &pin))) return rc;
+  WinAttnArgs a{};
+  a.T = T; a.n_seqs = L.n; a.H = s.heads; a.G = s.kv_heads; a.dim = s.dim; a.vdim = s.vdim;
+  a.window = s.window; a.chunk = s.chunk; a.softcap = s.softcap; a.sink = s.sink; a.qk_norm = s.qk_norm; a.own_kv = 1;
+  a.eps = h->cfg.norm_eps; a.scale = s.scale;
+  a.in_p = pin.p; a.in_S = pin.S; a.in_stride = pin.stride; a.in_ld = y.n_in;
+  a.slots = d + L.slots;
+  a.kpool = h->win_kpools[run_idx]; a.vpool = h->win_vpools[run_idx];
+  a.q = w.q; a.out = w.attn_out; a.o_ld = y.ov_p;
+  a.block_tables = d + L.block_tables; a.max_blocks = L.max_blocks;
+  a.cu_q = d + L.cu_q; a.seq_start = d + L.seq_start; a.seq_len = d + L.seq_len;
+  if (s.out_gate) { a.gate = w.att_gate; a.gate_ld = s.heads * s.vdim; }
+  if (L.prefill) {
+    a.tile_seq = d + L.tile_seq; a.tile_q0 = d + L.tile_q0; a.n_tiles = L.n_qtiles; a.qtile = h->attn_qtile;
+  } else {
+    a.n_tiles = L.n; a.qtile = 1;
+  }
+  ConvAttnPrep c{};
+  c.taps = s.conv; c.conv_w = y.conv_w; c.bias = s.proj_bias ? y.bias_in : nullptr;
+  c.qnorm_w = y.qnorm_w; c.knorm_w = y.knorm_w;
+  if (y.rope >= 0) {
+    const RopeTable& rt = h->ropes[y.rope];
+    c.rot_half = s.rot_dims / 2; c.cosT = rt.cosT; c.sinT = rt.sinT;
+  }
+  c.positions = d + L.positions; c.state_slots = d + L.state_slots;
+  c.state_pool = h->state_pool; c.slot_floats = h->state_slot_floats; c.tail_off = r.tail_off;
+  c.gate_out = s.out_gate ? w.att_gate : nullptr; c.gate_ld = a.gate_ld;
+  {
+    ProfScope ps(h, NVLLM_K_ROPE_KV,
+                 (double)T * y.n_in * 4 + (double)T * (y.n_q * asz + (y.n_k + y.n_v) * kvsz + (s.out_gate ? a.gate_ld * 4.0 : 0.0)), 0,
+                 (double)T * y.n_in * 4 * (pin.S - 1) + (double)T * y.conv_ch * 4 * (s.conv - 1));
+    LAUNCH(h, launch_winattn_prep_conv(h->stream, h->adt, h->kvdt, a, c));
+  }
+  {
+    // algorithmic: the visible K / V rows of every sequence once per step; flops over the visible pairs
+    const double span = s.chunk > 0 ? s.chunk : (s.window > 0 ? s.window : 1e30);
+    const double keys = std::min((double)L.sum_len, (double)L.n * (span - 1) + (double)T);
+    const double pairs = std::min(L.attn_pairs, (double)T * (s.chunk > 0 ? (span + 1) / 2 : span));
+    ProfScope ps(h, L.prefill ? NVLLM_K_ATTN_PREFILL : NVLLM_K_ATTN_DECODE, keys * s.kv_heads * (s.dim + s.vdim) * kvsz,
+                 2.0 * s.heads * (s.dim + s.vdim) * pairs, (double)T * (s.heads * s.dim + y.ov_p) * asz);
+    LAUNCH(h, launch_winattn(h->stream, h->adt, h->kvdt, a));
+  }
+  if ((rc = run_gemm(h, w.attn_out, y.ov_p, y.w_o, T, H, y.ov_p, 1.f, w.ws_b, w.ws_b_floats, H, pa))) return rc;
+  pa->m = s.mix_scale;
+  pa->bias = s.proj_bias ? y.o_bias : nullptr;
+  // ---- time mixing side: the five shifted inputs, a projection each into one row of partials
+  {
+    ProfScope ps(h, NVLLM_K_RECUR, (double)T * H * asz * 6 + 5.0 * H * 4, 0);
+    LAUNCH(h, launch_token_shift(h->stream, h->adt, T, L.n, H, 5, w.xn, y.mu, d + L.cu_q, d + L.positions, d + L.state_slots,
+                                 h->state_pool, h->state_slot_floats, r.shift_off, w.mx_in));
+  }
+  // the slot's tails move on: the attention side's convolution inputs (still in ws_a) and the token shift's last row
+  {
+    TailJob jobs[2];
+    int nj = 0;
+    if (s.conv > 1) {
+      TailJob& j = jobs[nj++];
+      j.seg = seg_of(pin, y.n_in, 0); j.bias = c.bias; j.act = nullptr;
+      j.channels = y.conv_ch; j.taps = s.conv; j.tail_off = r.tail_off;
+    }
+    TailJob& j = jobs[nj++];
+    j.seg = LinSeg{nullptr, 0, 0, 0}; j.bias = nullptr; j.act = w.xn;
+    j.channels = H; j.taps = 2; j.tail_off = r.shift_off;
+    ProfScope ps(h, NVLLM_K_RECUR, (double)L.n * ((s.conv - 1) * y.conv_ch + H) * 8, 0);
+    LAUNCH(h, launch_roll_tails(h->stream, h->adt, L.n, jobs, nj, d + L.cu_q, d + L.positions, d + L.state_slots,
+                                h->state_pool, h->state_slot_floats));
+  }
+  const int hd2 = s.heads2 * s.dim2;
+  Pending seg[5];
+  for (int i = 0; i < 5; i++) {
+    const int n = i < 4 ? hd2 : s.lowrank;
+    const char* A = (const char*)w.mx_in + (size_t)i * T * H * (size_t)asz;
+    const char* Wt = (const char*)y.w_in2 + (size_t)y.seg2[i] * H * wsz;
+    if ((rc = run_gemm(h, A, H, Wt, T, n, H, 1.f, w.ws_a + y.seg2[i], w.ws_a_floats - y.seg2[i], y.n_in2, &seg[i]))) return rc;
+  }
+  LinRecArgs b{};
+  linrec_common(h, &b, r);
+  b.H = s.heads2; b.dim = s.dim2; b.vdim = s.dim2; b.tmix = 1;
+  b.tau = 1.f; b.qmul = 1.f;
+  b.q = seg_of(seg[0], y.n_in2, 0); b.k = seg_of(seg[1], y.n_in2, 0); b.v = seg_of(seg[2], y.n_in2, 0);
+  b.gate = seg_of(seg[3], y.n_in2, 0); b.lr = seg_of(seg[4], y.n_in2, 0);
+  b.rank = s.lowrank; b.w2 = y.lr_w2; b.w2b = y.lr_b; b.bonus = y.bonus;
+  b.onorm_w = y.onorm_w; b.onorm_ld = s.dim2;
+  b.o_ld = y.ov2_p;
+  if ((rc = run_linrec(h, b, y.n_in2, seg[0].S))) return rc;
+  if ((rc = run_gemm(h, w.attn_out, y.ov2_p, y.w_o2, T, H, y.ov2_p, 1.f, w.ws_c, w.ws_b_floats, H, pb))) return rc;
+  pb->m = s.mix2_scale;
+  return NVLLM_OK;
+}
+
+// Mixture of squared-ReLU experts (+ the always-on expert): *p1 = the experts' outputs, combined
+// by the next norm kernel with the squared scores; *p2 = the always-on expert, times its gate there.
+static int ffn_moe_relu2(nvllm_handle* h, const ListedLayer& y, Pending* p1, Pending* p2) {
+  Workspace& w = h->ws;
+  const nvllm_layer_spec& s = y.s;
+  const int T = h->lay.T, H = h->H;
+  const double asz = dt_size(h->adt);
+  int rc;
+  if ((rc = run_moe_ffn(h, T, w.xn, s.experts, s.top, y.ff_p, 0.f, y.moe_in, y.moe_out, w.topk_w, p1, 2))) return rc;
+  if (s.shared_ff <= 0) return NVLLM_OK;
+  const int ff = y.sff_p;
+  Pending h1;
+  if ((rc = run_gemm(h, w.xn, H, y.w1, T, ff, H, 1.f, w.ws_a, w.ws_a_floats, ff, &h1, TC5_EPI_RELU2, w.hbuf, ff, nullptr)))
+    return rc;
+  if (h1.S > 0) {
+    ProfScope ps(h, NVLLM_K_ACT, (double)T * ff * (4 + asz), 0, (double)T * ff * 4 * (h1.S - 1));
+    LAUNCH(h, launch_act(h->stream, h->adt, T, ff, h1.p, h1.S, h1.stride, nullptr, 2, w.hbuf));
+  }
+  return run_gemm(h, w.hbuf, ff, y.w2, T, H, ff, 1.f, w.ws_b, w.ws_b_floats, H, p2);
+}
+
+// *row_m2_out: per-row multiplier of the second addend still pending at the end (or null)
+static int forward_layers_prenorm(nvllm_handle* h, Pending* p1, Pending* p2, const float** row_m2_out) {
+  const int T = h->lay.T;
+  const float* row_m2 = nullptr;  // per-row multiplier of the pending second addend
+  int rc;
+  for (size_t ri = 0; ri < h->runs.size(); ri++) {
+    const LayerRun& r = h->runs[ri];
+    const ListedLayer& y = h->ll[r.layer];
+    const float* xadd = r.pass_start >= 0 ? h->loop_step + (size_t)r.pass_start * h->H : nullptr;
+    if ((rc = run_prenorm(h, p1, p2, row_m2, xadd, y.post1_w, nullptr, T))) return rc;
+    row_m2 = nullptr;
+    Pending pa, pb;
+    if (y.s.mixer == NVLLM_MIXER_GLA) rc = mixer_gla(h, y, r, &pa);
+    else rc = mixer_attn_tmix(h, y, r, (int)ri, &pa, &pb);
+    if (rc) return rc;
+    if (y.s.mlp == NVLLM_MLP_MOE) {
+      if ((rc = run_prenorm(h, &pa, &pb, nullptr, nullptr, y.post2_w, &y, T))) return rc;
+      if ((rc = ffn_moe_relu2(h, y, p1, p2))) return rc;
+      row_m2 = p2->p ? h->ws.sh_gate : nullptr;
+    } else {
+      *p1 = pa;
+      *p2 = pb;
+    }
+  }
+  h->glu_limit_cur = 0.f;
+  *row_m2_out = row_m2;
+  return NVLLM_OK;
+}
+
 // ------------------------------------------------------------------ forward pass
 int forward_step_layered(nvllm_handle* h) {
   const StepLayout& L = h->lay;
@@ -468,12 +853,15 @@ int forward_step_layered(nvllm_handle* h) {
   }
   for (auto& r : h->ropes) {
     ProfScope ps(h, NVLLM_K_MISC, (double)T * r.dims * 4, 0);
-    LAUNCH(h, launch_rope_table(st, d_pos, T, r.dims / 2, r.inv_freq, r.cosT, r.sinT));
+    LAUNCH(h, launch_rope_table(st, d_pos, T, r.dims / 2, r.inv_freq, r.cosT, r.sinT, r.mult));
   }
   Pending p1, p2;
   int routed = 0;  // routed layers so far: picks the half of topk_w this layer writes
+  const float* row_m2 = nullptr;
   if (h->block_style == NVLLM_LBLOCK_SEQUENTIAL_POSTNORM) {
     if ((rc = forward_layers_postnorm(h))) return rc;
+  } else if (h->block_style == NVLLM_LBLOCK_SEQUENTIAL_PRENORM) {
+    if ((rc = forward_layers_prenorm(h, &p1, &p2, &row_m2))) return rc;
   } else
   for (int l = 0; l < h->L; l++) {
     const ListedLayer& y = h->ll[l];
@@ -583,7 +971,7 @@ int forward_step_layered(nvllm_handle* h) {
   }
   // final norm + LM head on the rows that were asked for: each sequence's last, then the extra ones
   if ((rc = run_norm(h, w.x, &p1, &p2, h->lnf_w, nullptr, w.xn_last, nullptr, d + L.last_row, n_out, nullptr,
-                     h->block_style == NVLLM_LBLOCK_PARALLEL_PRENORM)))
+                     h->block_style == NVLLM_LBLOCK_PARALLEL_PRENORM, row_m2)))
     return rc;
   Pending lg;
   if ((rc = run_gemm(h, w.xn_last, H, h->lm_head, n_out, h->V, H, 1.f, w.logits_p, w.logits_p_floats, h->ldl, &lg, 0,
@@ -622,9 +1010,37 @@ extern "C" int nvllm_create_layered(const nvllm_layered_config* c, const nvllm_l
   if (c->vocab_size <= 0 || c->hidden <= 0 || c->num_layers <= 0) return bad(-1, "non-positive dimension");
   if (c->hidden % 8) return bad(-1, "width must be a multiple of 8");
   if (c->precision != NVLLM_PREC_FP32 && c->precision != NVLLM_PREC_BF16) return bad(-1, "precision");
+  const bool pre_style = c->block_style == NVLLM_LBLOCK_SEQUENTIAL_PRENORM;
+  if (c->loop_times > 1 && (!pre_style || c->loop_start < 0 || c->loop_stop > c->num_layers || c->loop_start >= c->loop_stop))
+    return bad(-1, "a repeated run of layers needs the sequential pre-norm block style and 0 <= start < stop <= layers");
   for (int l = 0; l < c->num_layers; l++) {
     const nvllm_layer_spec& s = layers[l];
     const bool seq_style = c->block_style == NVLLM_LBLOCK_SEQUENTIAL_POSTNORM;
+    if (s.mixer == NVLLM_MIXER_GLA || s.mixer == NVLLM_MIXER_ATTN_TMIX) {
+      if (!pre_style) return bad(l, "gated linear attention / attention + time mixing need the sequential pre-norm block style");
+      if (s.heads <= 0 || s.dim <= 0 || s.vdim <= 0 || s.lowrank <= 0) return bad(l, "non-positive mixer size");
+      if (s.mixer == NVLLM_MIXER_GLA) {
+        if (s.dim > LINREC_MAX_DIM) return bad(l, "gated linear attention: dim <= 256");
+        if (!(s.tau > 0.f)) return bad(l, "gated linear attention: tau must be positive");
+      } else {
+        if (s.kv_heads <= 0 || s.heads % s.kv_heads) return bad(l, "heads must be a multiple of kv_heads");
+        if (s.heads2 <= 0 || s.dim2 <= 0 || s.dim2 > LINREC_MAX_DIM) return bad(l, "time mixing: heads2 > 0, 0 < dim2 <= 256");
+        if (s.conv < 1 || s.conv > 8) return bad(l, "convolution taps 1..8");
+        if (s.vdim > 512 || s.dim > 1024) return bad(l, "attention: dim <= 1024, vdim <= 512");
+        if (s.rot_dims < 0 || s.rot_dims > s.dim || (s.rot_dims & 1)) return bad(l, "rotated entries must be even and <= dim");
+        if (s.chunk < 0 || s.window < 0 || (s.chunk > 0 && s.window > 0)) return bad(l, "a chunked mask or a window, not both");
+        if (s.qk_norm != 2) return bad(l, "attention + time mixing: qk_norm = 2 (whole-row norms with weights)");
+      }
+      if (s.mlp != NVLLM_MLP_NONE && s.mlp != NVLLM_MLP_MOE) return bad(l, "pre-norm blocks: feed-forward none or mixture of experts");
+      if (s.mlp == NVLLM_MLP_MOE) {
+        if (s.act != NVLLM_FFN_RELU2 || !s.route_sigmoid || !s.weight_on_input)
+          return bad(l, "pre-norm blocks: squared-ReLU experts chosen by sigmoid scores, weight on the input");
+        if (s.ff <= 0 || s.experts <= 0 || s.experts > 256 || s.top <= 0 || s.top > 32 || s.top > s.experts || s.shared_ff < 0)
+          return bad(l, "ff > 0, experts 1..256, top 1..32");
+      }
+      continue;
+    }
+    if (pre_style) return bad(l, "this mixer has no sequential pre-norm form");
     if (s.mixer == NVLLM_MIXER_WINDOW_ATTENTION || s.mixer == NVLLM_MIXER_DELTA) {
       if (!seq_style) return bad(l, "window attention / delta rule mixers need the sequential post-norm block style");
       if (s.heads <= 0 || s.kv_heads <= 0 || s.dim <= 0 || s.vdim <= 0) return bad(l, "non-positive mixer size");
@@ -714,6 +1130,14 @@ extern "C" int nvllm_create_layered(const nvllm_layered_config* c, const nvllm_l
   h->block_style = c->block_style;
   h->position_kind = c->position;
   h->norm_offset = c->norm_offset;
+  if (pre_style) {
+    g.num_kv_heads = layers[0].kv_heads > 0 ? layers[0].kv_heads : layers[0].heads; g.head_dim = layers[0].dim;
+    g.attention_type = NVLLM_ATTN_GQA; g.norm_type = NVLLM_NORM_RMS; g.position_type = NVLLM_POS_ROPE;
+    g.activation_type = NVLLM_ACT_GELU; g.block_style = NVLLM_BLOCK_SEQUENTIAL;
+    if (c->loop_times > 1) {
+      h->loop_start = c->loop_start; h->loop_stop = c->loop_stop; h->loop_times = c->loop_times;
+    }
+  }
   h->num_state_slots = c->num_state_slots > 0 ? c->num_state_slots : g.max_num_seqs;
   h->spec_enabled = 0;  // the speculative next step is keyed on the uniform models' shapes
   if (const char* env = getenv("NVLLM_SKIP")) h->skip_mask = (unsigned)strtoul(env, nullptr, 0);
@@ -752,6 +1176,89 @@ extern "C" int nvllm_create_layered(const nvllm_layered_config* c, const nvllm_l
     ListedLayer& y = h->ll[l];
     y.s = layers[l];
     const nvllm_layer_spec& s = y.s;
+    if (s.mixer == NVLLM_MIXER_GLA || s.mixer == NVLLM_MIXER_ATTN_TMIX) {
+      const int hd = s.heads * s.dim, hv = s.heads * s.vdim;
+      y.ov_p = (int)up8((size_t)hv);
+      y.ff_p = (int)up8((size_t)std::max(s.ff, 0));
+      AL(y.post1_w, (size_t)W * 4);
+      if (s.mixer == NVLLM_MIXER_GLA) {
+        y.n_in = 2 * hd + 2 * hv + s.lowrank;  // q | k | v | gate | decay inner
+        AL(y.w_in, (size_t)y.n_in * W * wsz);
+        AL(y.lr_w2, (size_t)hd * s.lowrank * 4);
+        AL(y.lr_b, (size_t)hd * 4);
+        AL(y.onorm_w, (size_t)s.vdim * 4);
+        q_cols = std::max(q_cols, y.ov_p);
+      } else {
+        const int hd2 = s.heads2 * s.dim2;
+        y.n_q = hd; y.n_k = s.kv_heads * s.dim; y.n_v = s.kv_heads * s.vdim;
+        y.conv_ch = y.n_q + y.n_k + y.n_v;
+        y.n_in = y.conv_ch + (s.out_gate ? hv : 0);  // Q | K | V | gate
+        AL(y.w_in, (size_t)y.n_in * W * wsz);
+        AL(y.bias_in, (size_t)y.n_in * 4);
+        AL(y.o_bias, (size_t)W * 4);
+        AL(y.qnorm_w, (size_t)y.n_q * 4);
+        AL(y.knorm_w, (size_t)y.n_k * 4);
+        AL(y.conv_w, (size_t)y.conv_ch * s.conv * 4);
+        // time mixing: five projections, each on its own input, into one row of partials
+        int off = 0;
+        for (int i = 0; i < 5; i++) {
+          y.seg2[i] = off;
+          off += (int)up8((size_t)(i < 4 ? hd2 : s.lowrank));
+        }
+        y.n_in2 = off;
+        y.ov2_p = (int)up8((size_t)hd2);
+        AL(y.w_in2, (size_t)y.n_in2 * W * wsz);
+        AL(y.w_o2, (size_t)W * y.ov2_p * wsz);
+        AL(y.lr_w2, (size_t)hd2 * s.lowrank * 4);
+        AL(y.lr_b, (size_t)hd2 * 4);
+        AL(y.mu, (size_t)5 * W * 4);
+        AL(y.bonus, (size_t)hd2 * 4);
+        AL(y.onorm_w, (size_t)hd2 * 4);
+        if (s.rot_dims > 0) {
+          for (size_t r = 0; r < h->ropes.size(); r++) {
+            const RopeTable& t = h->ropes[r];
+            if (t.base == (double)s.rot_base && t.dims == s.rot_dims && t.factor == (double)s.rot_factor &&
+                t.original == (double)s.rot_original && t.fast == (double)s.rot_fast && t.slow == (double)s.rot_slow)
+              y.rope = (int)r;
+          }
+          if (y.rope < 0) {
+            RopeTable rt;
+            rt.base = s.rot_base; rt.dims = s.rot_dims;
+            rt.factor = s.rot_factor; rt.original = s.rot_original; rt.fast = s.rot_fast; rt.slow = s.rot_slow;
+            y.rope = (int)h->ropes.size();
+            h->ropes.push_back(rt);
+          }
+        }
+        const int qt = winattn_qtile(h->adt, h->kvdt, s.dim, s.vdim);
+        win_qtile = win_qtile ? std::min(win_qtile, qt) : qt;
+        qkv_cols = std::max(qkv_cols, y.n_in2);
+        q_cols = std::max(q_cols, std::max(y.n_q, std::max(y.ov_p, y.ov2_p)));
+        h->nh = std::max(h->nh, s.heads2);
+      }
+      AL(y.w_o, (size_t)W * y.ov_p * wsz);
+      if (s.mlp == NVLLM_MLP_MOE) {
+        AL(y.post2_w, (size_t)W * 4);
+        AL(y.router, (size_t)s.experts * W * 4);
+        AL(y.moe_in, (size_t)s.experts * y.ff_p * W * wsz);
+        AL(y.moe_out, (size_t)s.experts * W * y.ff_p * wsz);
+        h->moe = true;
+        h->E = std::max(h->E, s.experts);
+        h->topk = std::max(h->topk, s.top);
+        h->F = std::max(h->F, y.ff_p);
+        if (s.shared_ff > 0) {
+          y.sff_p = (int)up8((size_t)s.shared_ff);
+          AL(y.w1, (size_t)y.sff_p * W * wsz);
+          AL(y.w2, (size_t)W * y.sff_p * wsz);
+          AL(y.sh_gate, (size_t)W * 4);
+          h->F = std::max(h->F, y.sff_p);
+          qkv_cols = std::max(qkv_cols, y.sff_p);
+        }
+      }
+      qkv_cols = std::max(qkv_cols, y.n_in);
+      h->nh = std::max(h->nh, s.heads);
+      h->hd = std::max(h->hd, s.vdim);
+      continue;
+    }
     if (s.mixer != NVLLM_MIXER_LATENT_ATTENTION) {
       const bool delta = s.mixer == NVLLM_MIXER_DELTA;
       const int own = s.kv_from < 0;
@@ -840,6 +1347,30 @@ extern "C" int nvllm_create_layered(const nvllm_layered_config* c, const nvllm_l
     q_cols = std::max(q_cols, s.heads * y.Dk);
     h->nh = std::max(h->nh, s.heads);
     h->hd = std::max(h->hd, s.kv_rank);
+  }
+  if (pre_style) {
+    // the executions of a step in order; every one gets its own piece of a state slot
+    auto add_run = [&](int l, int pass_start) {
+      LayerRun r;
+      r.layer = l; r.pass_start = pass_start;
+      const nvllm_layer_spec& s = h->ll[l].s;
+      r.state_off = h->state_slot_floats;
+      if (s.mixer == NVLLM_MIXER_GLA) {
+        h->state_slot_floats += (size_t)s.heads * s.dim * s.vdim;
+      } else {
+        r.tail_off = r.state_off + (size_t)s.heads2 * s.dim2 * s.dim2;
+        r.shift_off = r.tail_off + (size_t)(s.conv - 1) * h->ll[l].conv_ch;
+        h->state_slot_floats = r.shift_off + (size_t)W;
+      }
+      h->runs.push_back(r);
+    };
+    const bool loop = h->loop_times > 1;
+    const int a0 = loop ? h->loop_start : 0, a1 = loop ? h->loop_stop : 0;
+    for (int l = 0; l < a0; l++) add_run(l, -1);
+    for (int t = 0; t < (loop ? h->loop_times : 0); t++)
+      for (int l = a0; l < a1; l++) add_run(l, l == a0 ? t : -1);
+    for (int l = a1; l < h->L; l++) add_run(l, -1);
+    if (loop) AL(h->loop_step, (size_t)h->loop_times * W * 4);
   }
 #undef AL
   h->attn_qtile = win_qtile ? win_qtile : latent_attn_qtile();

@@ -214,7 +214,7 @@ static bool resid_gemm_ok(const nvllm_handle* h, int M, int N, int K, int lda) {
 
 static int run_norm(nvllm_handle* h, float* x, Pending* p1, Pending* p2, const float* w,
                     const float* b, void* y, float* y_f32, const int* row_idx, int n_rows,
-                    const RouterArgs* route = nullptr, bool centered = false) {
+                    const RouterArgs* route = nullptr, bool centered = false, const float* row_m2 = nullptr) {
   NormArgs a{};
   a.centered = centered ? 1 : 0;
   a.x = x;
@@ -236,6 +236,7 @@ static int run_norm(nvllm_handle* h, float* x, Pending* p1, Pending* p2, const f
     return set_err(h, NVLLM_ERR_INVALID, "MoE layers in a parallel block are not supported");
   if (p2 && p2->p) {
     a.p2 = p2->p; a.S2 = p2->S; a.stride2 = p2->stride; a.m2 = p2->m; a.bias2 = p2->bias;
+    a.row_m2 = row_m2;
     bytes += (double)n_rows * h->H * 4;
     impl += (double)n_rows * h->H * 4 * (p2->S - 1);
   }
@@ -253,10 +254,11 @@ static int run_norm(nvllm_handle* h, float* x, Pending* p1, Pending* p2, const f
 // kernel that produced xn): group the (token, slot) pairs by expert, two grouped GEMMs with the
 // gated unit between them.  E experts of inner size I, k per token; glu_limit > 0 selects the
 // clamped gated unit; topk_w holds this layer's routing weights.  Leaves the expert outputs
-// pending in *pf (combined by the next norm).
+// pending in *pf (combined by the next norm).  act = 2: experts W_down relu(W_up x)^2 — moe_in
+// stacks [I, H] matrices instead of interleaved [2 I, H] ones.
 static int run_moe_ffn(nvllm_handle* h, int T, const void* xn, int E, int k, int I, float glu_limit,
                        const void* moe_in, const void* moe_out, const float* topk_w,
-                       Pending* pf) {
+                       Pending* pf, int act = 1) {
   const int H = h->H;
   const int P = T * k;
   Workspace& w = h->ws;
@@ -264,7 +266,8 @@ static int run_moe_ffn(nvllm_handle* h, int T, const void* xn, int E, int k, int
   const double asz = dt_size(h->adt);
   // bf16 mode: grouped tcgen05 GEMMs over the expert-sorted rows; fp32 parity mode (and
   // shapes TMA cannot address): the SIMT fp32 tiles
-  const bool tc = h->adt == DT_BF16 && h->wdt == DT_BF16 && tc5_supported(P, 2 * I, H) &&
+  const int N1 = act == 2 ? I : 2 * I;  // columns of the experts' first projection
+  const bool tc = h->adt == DT_BF16 && h->wdt == DT_BF16 && tc5_supported(P, N1, H) &&
                   tc5_supported(P, H, I) && (I % 8) == 0;
   const int tile = tc ? tc5_group_tile((P + E - 1) / E) : 64;
   // the routing itself (softmax, top-k) ran inside the FFN norm kernel above
@@ -285,13 +288,13 @@ static int run_moe_ffn(nvllm_handle* h, int T, const void* xn, int E, int k, int
       LAUNCH(h, launch_moe_gather(st, P, H, xn, w.sort.a_rows, w.moe_xs));
     }
     Tc5Args t{};
-    t.A = w.moe_xs; t.W = moe_in; t.M = P; t.N = 2 * I; t.K = H;
-    t.S = 1; t.alpha = 1.f; t.epi = TC5_EPI_SWIGLU; t.glu_limit = glu_limit; t.epi_out = w.hbuf; t.epi_ld = I;
+    t.A = w.moe_xs; t.W = moe_in; t.M = P; t.N = N1; t.K = H;
+    t.S = 1; t.alpha = 1.f; t.epi = act == 2 ? TC5_EPI_RELU2 : TC5_EPI_SWIGLU; t.glu_limit = glu_limit; t.epi_out = w.hbuf; t.epi_ld = I;
     t.g_experts = E; t.g_tile = tile; t.g_max_tiles = w.max_tiles;
     t.g_tile_expert = w.sort.tile_expert; t.g_tile_row0 = w.sort.tile_row0;
     t.g_tile_rows = w.sort.tile_rows; t.g_n_tiles = w.sort.n_tiles;
     {
-      ProfScope ps(h, NVLLM_K_MOE_GEMM, (double)e_touched * 2 * I * H * wsz, 2.0 * P * 2 * I * H,
+      ProfScope ps(h, NVLLM_K_MOE_GEMM, (double)e_touched * N1 * H * wsz, 2.0 * P * N1 * H,
                    (double)P * H * asz + (double)P * I * asz);
       LAUNCH(h, launch_gemm_tc5(st, t, nullptr));
     }
@@ -307,19 +310,20 @@ static int run_moe_ffn(nvllm_handle* h, int T, const void* xn, int E, int k, int
   } else {
     GemmArgs g{};
     g.A = xn; g.adt = h->adt; g.lda = H; g.W = moe_in; g.wdt = h->wdt;
-    g.M = P; g.N = 2 * I; g.K = H; g.out = w.ws_a; g.ldo = 2 * I; g.alpha = 1.f;
+    g.M = P; g.N = N1; g.K = H; g.out = w.ws_a; g.ldo = N1; g.alpha = 1.f;
     g.a_rows = w.sort.a_rows; g.tile_expert = w.sort.tile_expert; g.tile_row0 = w.sort.tile_row0;
     g.tile_rows = w.sort.tile_rows; g.n_tiles = w.sort.n_tiles;
-    g.expert_stride = (size_t)2 * I * H; g.max_tiles = w.max_tiles;
+    g.expert_stride = (size_t)N1 * H; g.max_tiles = w.max_tiles;
     {
       ProfScope ps(h, NVLLM_K_MOE_GEMM,
-                   (double)e_touched * 2 * I * H * wsz + (double)P * H * asz + (double)P * 2 * I * 4,
-                   2.0 * P * 2 * I * H);
+                   (double)e_touched * N1 * H * wsz + (double)P * H * asz + (double)P * N1 * 4,
+                   2.0 * P * N1 * H);
       LAUNCH(h, launch_gemm_simt(st, g));
     }
     {
-      ProfScope ps(h, NVLLM_K_MOE_MISC, (double)P * I * (8 + asz), 0);
-      LAUNCH(h, launch_moe_glu(st, h->adt, P, I, w.ws_a, w.hbuf, glu_limit));
+      ProfScope ps(h, NVLLM_K_MOE_MISC, (double)P * (N1 * 4 + I * asz), 0);
+      if (act == 2) LAUNCH(h, launch_act(st, h->adt, P, I, w.ws_a, 1, 0, nullptr, 2, w.hbuf));
+      else LAUNCH(h, launch_moe_glu(st, h->adt, P, I, w.ws_a, w.hbuf, glu_limit));
     }
     GemmArgs g2{};
     g2.A = w.hbuf; g2.adt = h->adt; g2.lda = I; g2.W = moe_out; g2.wdt = h->wdt;

@@ -66,11 +66,39 @@ struct ListedLayer {
   float *a_log = nullptr, *dt_bias = nullptr, *onorm_w = nullptr;  // [heads], [heads], [vdim] fp32
   size_t state_off = 0;            // floats from a slot's base to this layer's [heads][dim][vdim] state
   size_t tail_off = 0;             // ... and to its convolution tail [taps - 1][conv_ch]
+  // ---- sequential pre-norm blocks (forward_layered.cu): norm weights in post1_w / post2_w
+  // gated linear attention: fused projection rows [q | k | v | gate | decay inner (lowrank)]
+  // attention + time mixing: attention projection rows [Q | K | V | gate] in w_in with bias_in, W_o in
+  //   w_o with o_bias; time mixing's five projections [r | k | v | gate | decay inner] in w_in2 (each
+  //   reads its own token-shift mix; segment s starts at row / column seg2[s], a multiple of 8), W_o in w_o2
+  float *bias_in = nullptr, *o_bias = nullptr;   // [n_in] (zeros past q, k, v), [W]
+  float *qnorm_w = nullptr, *knorm_w = nullptr;  // [n_q], [n_k] whole-row norms
+  float *lr_w2 = nullptr, *lr_b = nullptr;       // decay: second step [heads dim, lowrank] and its additive term, fp32
+  float *mu = nullptr, *bonus = nullptr;         // time mixing: [5][W] shift weights (r, k, v, gate, decay), [heads2, dim2]
+  void *w_in2 = nullptr, *w_o2 = nullptr;
+  int n_in2 = 0, ov2_p = 0;
+  int seg2[5] = {0, 0, 0, 0, 0};
+  // mixture of squared-ReLU experts: moe_in [experts, ff_p, W], moe_out [experts, W, ff_p]; the
+  // always-on expert in w1 [sff_p, W] / w2 [W, sff_p] with its gate row sh_gate [W] fp32
+  float* sh_gate = nullptr;
+  int sff_p = 0;
+};
+// One execution of a layer: a layer inside a repeated run of layers executes once per pass, every
+// time with caches and state of its own.
+struct LayerRun {
+  int layer = 0;
+  int pass_start = -1;   // >= 0: this run opens pass `pass_start` (the pass's vector is added to x first)
+  size_t state_off = 0;  // recurrent state [heads][dim][vdim] (time mixing: [heads2][dim2][dim2]) inside a slot
+  size_t tail_off = 0;   // attention side: convolution tail [taps - 1][n_q + n_k + n_v]
+  size_t shift_off = 0;  // time mixing: the previous token's input [W]
 };
 struct RopeTable {
   double base = 0;
   int dims = 0;
   double* inv_freq = nullptr;  // [dims / 2] on the device
+  // interpolated frequencies (factor > 0): entry i keeps f_i where its wavelength is short, takes
+  // f_i / factor where it is long, a linear ramp between; mult multiplies cos and sin
+  double factor = 0, original = 0, fast = 0, slow = 0, mult = 1.0;
   float *cosT = nullptr, *sinT = nullptr;  // [T_cap, dims / 2] of the current step's rows
 };
 
@@ -134,6 +162,11 @@ struct Workspace {
   // delta rule (forward_layered.cu): conv + activation output [T, max conv_ch], per-head step
   // inputs [T, 2 max heads] (write strength | decay), read-outs [T, max heads * vdim], all fp32
   float *dl_qkv = nullptr, *dl_bg = nullptr, *dl_o = nullptr;
+  // linear recurrences (linrec.cu): q | k | decay [T, 3 max heads dim], values and read-outs [T, max heads vdim] fp32;
+  // time mixing's five shifted inputs [5][T][W] act dtype; attention output gates [T, max heads vdim] and
+  // the always-on expert's gate [T] fp32
+  float *lr_qkw = nullptr, *lr_v = nullptr, *lr_o = nullptr, *att_gate = nullptr, *sh_gate = nullptr;
+  void* mx_in = nullptr;
   float* moe_Y = nullptr;  // [T k, H]
   float* moe_y = nullptr;  // [T, H]
   void* moe_xs = nullptr;  // [T k, H] bf16: normed activations in expert-sorted order
@@ -196,6 +229,11 @@ struct nvllm_handle {
   std::vector<void*> lat_pools;          // per cache-owning layer: [num_blocks * 256][Dk]
   // window attention: per cache-owning layer K [num_blocks][kv_heads][256][dim], V [...][vdim]
   std::vector<void*> win_kpools, win_vpools;
+  // sequential pre-norm blocks: the layer executions of a step in order (K / V pools above are
+  // indexed by execution there), the vectors that open the passes of the repeated run [times][W]
+  std::vector<nvllm::LayerRun> runs;
+  float* loop_step = nullptr;
+  int loop_start = 0, loop_stop = 0, loop_times = 1;
   int block_style = 0, position_kind = 0;
   float norm_offset = 0.f;               // added to every norm weight at load
   double* pos_freq = nullptr;            // sinusoidal positions: 10000^(-2i / W), i < W / 2, on the device

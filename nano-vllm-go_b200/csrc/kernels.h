@@ -39,9 +39,13 @@ cudaError_t launch_embed(cudaStream_t st, int wdt, const int* tokens, const int*
 // experts (moe.go:88-103).  groups > 0: the experts form `groups` equal groups of neighbours, a
 // group scores as its best expert and only the `keep` best groups may be chosen from.
 // raw != 0: the weights are the chosen experts' softmax scores times `scale`, not renormalised.
+// sigmoid != 0: an expert's score is sigmoid(logit) on its own (no softmax over the experts).
+// square != 0: the weight written is the square of that (a weight w on the INPUT of an expert
+// W_down relu(W_up .)^2 equals w^2 on its output, for w > 0).
 struct RouteOpts {
   int groups, keep, raw;
   float scale;
+  int sigmoid, square;
 };
 struct NormArgs {
   float* x;            // [*, H] residual stream, updated in place when p1/p2 given
@@ -84,6 +88,14 @@ struct NormArgs {
   int* topk_idx;
   float* topk_w;
   RouteOpts route;
+  // a pre-norm block that repeats: xadd [H] is added to the row with the pending results (the
+  // vector a pass starts with); row_m2 [rows] multiplies the second addend row by row (an
+  // always-on expert with a gate per token); gate_w [H] != null: gate_out[row] =
+  // sigmoid(normed row . gate_w) for that expert's next run
+  const float* xadd;
+  const float* row_m2;
+  const float* gate_w;
+  float* gate_out;
 };
 cudaError_t launch_norm(cudaStream_t st, const NormArgs& a);
 
@@ -385,8 +397,9 @@ struct LatentArgs {
   float* split_ws;                   // [T, H, n_splits, R + 2]
   void* olat;                        // [T, o_ld] act dtype: gate * sum p c per head = input of the folded output projection
 };
+// mult multiplies both cos and sin (a rotation whose frequencies were interpolated)
 cudaError_t launch_rope_table(cudaStream_t st, const int* positions, int T, int half,
-                              const double* inv_freq, float* cosT, float* sinT);
+                              const double* inv_freq, float* cosT, float* sinT, double mult = 1.0);
 cudaError_t launch_latent_prep(cudaStream_t st, int qdt, int kvdt, const LatentArgs& a);
 cudaError_t launch_latent_q(cudaStream_t st, int qdt, const LatentArgs& a);
 // once per layer at finalize: wq [H (R + rot), q_rank_p] and wo [W, ovr_p] from the four checkpoint
@@ -408,6 +421,10 @@ struct WinAttnArgs {
   int T, n_seqs;
   int H, G, dim, vdim;   // query heads, key / value heads, query-key and value entries per head
   int window;            // position i sees j with 0 <= i - j < window; 0: every j <= i
+  int chunk;             // > 0: position i sees j <= i with i / chunk == j / chunk (instead of a window)
+  float softcap;         // > 0: score <- softcap * tanh(score / softcap)
+  const float* gate;     // [T, gate_ld] or null: output (t, head, col) times gate[t][head * vdim + col]
+  int gate_ld;
   int sink, qk_norm, own_kv;
   float eps, scale;
   // fused projection [Q heads | K heads | V heads] (K / V only with own_kv): split-K partials [S][T][in_ld]
@@ -422,6 +439,25 @@ struct WinAttnArgs {
   int n_tiles, qtile;
 };
 cudaError_t launch_winattn_prep(cudaStream_t st, int qdt, int kvdt, const WinAttnArgs& a);
+// Projection epilogue of an attention whose q, k, v pass a short causal convolution over time:
+// fused projection columns [Q | K | V | gate (H vdim, when gate_out)]; per token: split-K sum + bias,
+// convolution (taps inputs; those before the step's first token come from the sequence's state
+// slot, zeros before the sequence's start), RMS norm over the WHOLE q row and the whole k row with
+// weights, rotation of the first 2 * rot_half entries of every head (entry i with i + rot_half),
+// Q to the activation dtype, K / V into the pools; gate_out = sigmoid of the gate columns.
+struct ConvAttnPrep {
+  int taps;
+  const float* conv_w;   // [n_q + n_k + n_v, taps]
+  const float* bias;     // [n_q + n_k + n_v] or null
+  const float *qnorm_w, *knorm_w;  // [n_q], [n_k]
+  int rot_half;
+  const float *cosT, *sinT;        // [T, rot_half] of the step's rows
+  const int *positions;            // [T]
+  const int* state_slots;          // [n_seqs]
+  const float* state_pool; size_t slot_floats, tail_off;  // tail [taps - 1][n_q + n_k + n_v] inside a slot
+  float* gate_out; int gate_ld;
+};
+cudaError_t launch_winattn_prep_conv(cudaStream_t st, int qdt, int kvdt, const WinAttnArgs& a, const ConvAttnPrep& c);
 cudaError_t launch_winattn(cudaStream_t st, int qdt, int kvdt, const WinAttnArgs& a);
 // queries per tile of the kernel launch_winattn picks for a prefill step (the host builds the tile list with it)
 int winattn_qtile(int qdt, int kvdt, int dim, int vdim);
@@ -448,6 +484,57 @@ struct DeltaArgs {
 cudaError_t launch_delta_prep(cudaStream_t st, const DeltaArgs& a);
 cudaError_t launch_delta_scan(cudaStream_t st, const DeltaArgs& a);
 cudaError_t launch_delta_out(cudaStream_t st, int odt, const DeltaArgs& a);
+
+// ---------------------------------------------------------------- linrec.cu
+// Linear recurrences with a diagonal decay, per head a dim x vdim state in fp32 kept per state slot:
+//   gated linear attention   S <- diag(a_t) S + k_t v_t^T,  o_t = S^T q_t
+//   time mixing              o_t = (S + diag(u) k_t v_t^T)^T r_t,  then S <- diag(w_t) S + k_t v_t^T
+// between their projections.  A projection's result is a segment of split-K partials.
+struct LinSeg {
+  const float* p;   // element (t, c) = sum_s p[s * stride + t * ld + c]
+  int S;
+  size_t stride;
+  int ld;
+};
+struct LinRecArgs {
+  int T, n_seqs;
+  int H, dim, vdim;
+  int tmix;              // 0: gated linear attention, 1: time mixing (read before the update, bonus u)
+  float eps, tau, qmul;  // q <- q * qmul; gated linear attention: decay = sigmoid(z)^(1 / tau)
+  LinSeg q, k, v, lr, gate;  // lr [T, rank]: inner result of the decay's two-step projection
+  int rank;
+  const float* w2;       // [H dim, rank] fp32; z = w2 f(lr) + w2b, f = tanh for time mixing
+  const float* w2b;      // [H dim]
+  const float* bonus;    // [H, dim] (time mixing)
+  const float* onorm_w;  // weight of the read-out's RMS norm over vdim
+  int onorm_ld;          // 0: one [vdim] weight shared by the heads; vdim: a weight per head
+  const int *cu_q, *positions, *state_slots;  // [n_seqs + 1], [T], [n_seqs]
+  float* state_pool; size_t slot_floats, state_off;  // this layer's [H][dim][vdim] inside a slot
+  float* qkw;            // [T, 3 H dim]: q | k | decay
+  float* vv;             // [T, H vdim]
+  float* o;              // [T, H vdim] read-outs
+  void* out; int o_ld;   // [T, o_ld] act dtype: normed, gated read-outs = input of the output projection
+};
+cudaError_t launch_linrec_prep(cudaStream_t st, const LinRecArgs& a);
+cudaError_t launch_linrec_scan(cudaStream_t st, const LinRecArgs& a);
+cudaError_t launch_linrec_out(cudaStream_t st, int odt, const LinRecArgs& a);
+constexpr int LINREC_MAX_DIM = 256;
+// Token shift: out[s][t][:] = h_t + (h_{t-1} - h_t) * mu[s][:] for s < n_mix (act dtype, [n_mix][T][W]);
+// h_{t-1} of a step's first row comes from the sequence's slot (tail [W]), zeros at position 0.
+cudaError_t launch_token_shift(cudaStream_t st, int adt, int T, int n_seqs, int W, int n_mix, const void* h,
+                               const float* mu, const int* cu_q, const int* positions, const int* state_slots,
+                               const float* state_pool, size_t slot_floats, size_t tail_off, void* out);
+// After a step: the last taps - 1 inputs of every sequence become its slot's tail [taps - 1][channels].
+// Source: split-K partials (+ bias) when seg.p, else rows of `act` (act dtype, row stride channels).
+struct TailJob {
+  LinSeg seg;
+  const float* bias;
+  const void* act;
+  int channels, taps;
+  size_t tail_off;
+};
+cudaError_t launch_roll_tails(cudaStream_t st, int adt, int n_seqs, const TailJob* jobs, int n_jobs, const int* cu_q,
+                              const int* positions, const int* state_slots, float* state_pool, size_t slot_floats);
 
 // ---------------------------------------------------------------- mamba.cu
 // Mamba2 block between its two projections (mamba2.go:72-351), ragged batch

@@ -1,0 +1,365 @@
+// linrec.cu — linear recurrences with a diagonal decay, for the layers of a model given as a list
+// (nvllm_mixer_kind NVLLM_MIXER_GLA and the time-mixing side of NVLLM_MIXER_ATTN_TMIX).
+//
+// Per head a dim x vdim state S in fp32, zero at a sequence's start, kept per state slot:
+//   gated linear attention   a_t = sigmoid(z_t)^(1 / tau),  S <- diag(a_t) S + k_t v_t^T,  o_t = S^T q_t
+//   time mixing              w_t = exp(-exp(z_t)),  o_t = (S + diag(u) k_t v_t^T)^T r_t,  S <- diag(w_t) S + k_t v_t^T
+// with z_t = W_2 f(W_1 x_t) + b per (head, key entry): f = identity / tanh.  The decay rows belong to
+// key entries.  The read-out of a head is divided by its root mean square, multiplied by a weight
+// and by silu(gate) and goes to the output projection.
+//
+//   linrec_prep_kernel   per token: split-K sums of the projections, q scaled, the second step of
+//                        the decay's projection (fp32 FMA, rank is small) and the decay itself —
+//                        logarithms, exponentials and sigmoids in fp32 (log-sigmoid form, no overflow).
+//   linrec_scan_kernel   CTA = (sequence, head, 128 / LPC value columns).  A column of the state is
+//                        independent of the others: it lives in the registers of LPC lanes
+//                        (RPL rows each, rows dealt in groups of four so that the lanes' 16-byte
+//                        shared-memory reads of q / k / decay do not collide); per token one
+//                        pass over the rows and log2(LPC) shuffles.  Token inputs are staged
+//                        through shared memory in chunks, the next chunk's loads are in flight
+//                        (cp.async) while the current one is scanned.  State read from the slot when the sequence
+//                        has earlier tokens, written back at the end.
+//   linrec_out_kernel    per token, a warp per head: RMS over vdim, weight, silu(gate) -> act dtype.
+//   token_shift_kernel   the inputs of time mixing's projections: h_t + (h_{t-1} - h_t) mu_s.
+//   roll_tails_kernel    after a step, the last inputs of a short convolution / token shift become
+//                        the slot's tail (one thread per channel reads all it needs, then writes).
+#include <stdlib.h>
+
+#include <algorithm>
+
+#include "common.cuh"
+#include "kernels.h"
+#include "mma.cuh"
+
+namespace nvllm {
+
+namespace {
+__device__ __forceinline__ int lr_seq_of_row(const int* __restrict__ cu_q, int n_seqs, int row) {
+  int lo = 0, hi = n_seqs - 1;  // last s with cu_q[s] <= row
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (cu_q[mid] <= row) lo = mid;
+    else hi = mid - 1;
+  }
+  return lo;
+}
+__device__ __forceinline__ float seg_at(const LinSeg& g, int t, int c) {
+  const float* p = g.p + (size_t)t * g.ld + c;
+  float acc = 0.f;
+  for (int s = 0; s < g.S; s++) acc += p[(size_t)s * g.stride];
+  return acc;
+}
+__device__ __forceinline__ void lr_cp_async4(uint32_t dst, const void* src, bool ok) {
+  const int n = ok ? 4 : 0;  // src-size 0: the destination is filled with zeros
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+}  // namespace
+
+// ------------------------------------------------------------------ projections' epilogue
+// grid (T, Y), 256 threads; channel c of the H * dim key entries: q, k, decay; then the values.
+__global__ void __launch_bounds__(256) linrec_prep_kernel(LinRecArgs a, Trace tr) {
+  TRACE_ENTRY(tr);
+  pdl_launch_dependents();
+  extern __shared__ float lr[];  // [rank]
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int hd = a.H * a.dim, hv = a.H * a.vdim;
+  for (int r = threadIdx.x; r < a.rank; r += blockDim.x) {
+    const float x = seg_at(a.lr, t, r);
+    lr[r] = a.tmix ? tanhf(x) : x;
+  }
+  __syncthreads();
+  float* qkw = a.qkw + (size_t)t * 3 * hd;
+  const float inv_tau = 1.0f / a.tau;
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < hd; c += gridDim.y * blockDim.x) {
+    const float* w = a.w2 + (size_t)c * a.rank;
+    float z = 0.f;
+    for (int r = 0; r < a.rank; r++) z = fmaf(w[r], lr[r], z);
+    z += a.w2b[c];
+    float decay;
+    if (a.tmix) {
+      decay = expf(-expf(z));
+    } else {
+      // sigmoid(z)^(1 / tau) = exp(log sigmoid(z) / tau), log sigmoid(z) = min(z, 0) - log1p(exp(-|z|))
+      const float ls = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
+      decay = expf(ls * inv_tau);
+    }
+    qkw[c] = seg_at(a.q, t, c) * a.qmul;
+    qkw[hd + c] = seg_at(a.k, t, c);
+    qkw[2 * hd + c] = decay;
+  }
+  float* vv = a.vv + (size_t)t * hv;
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < hv; c += gridDim.y * blockDim.x) vv[c] = seg_at(a.v, t, c);
+  TRACE_EXIT(tr);
+}
+
+cudaError_t launch_linrec_prep(cudaStream_t st, const LinRecArgs& a) {
+  if (a.T <= 0) return cudaSuccess;
+  const int big = std::max(a.H * a.dim, a.H * a.vdim);
+  const dim3 grid(a.T, a.T >= 1024 ? 1 : std::min(8, ceil_div(big, 256)));
+  (void)launch_k(linrec_prep_kernel, grid, dim3(256), (size_t)a.rank * sizeof(float), st, a, next_trace(40));
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------ scan over tokens
+constexpr int LR_THREADS = 128;
+
+template <int RPL, int LPC, bool TMIX>
+__global__ void __launch_bounds__(LR_THREADS) linrec_scan_kernel(LinRecArgs a, Trace tr) {
+  TRACE_ENTRY(tr);
+  pdl_launch_dependents();
+  constexpr int DP = RPL * LPC;          // rows of the state, padded
+  constexpr int VC = LR_THREADS / LPC;   // value columns of this CTA
+  constexpr int TC = DP >= 256 ? 4 : (DP >= 128 ? 8 : 16);  // tokens per staged chunk
+  constexpr int ROW = 3 * DP + VC;       // floats of one staged token: q | k | decay | v
+  __shared__ __align__(16) float stage[2][TC][ROW];
+  const int seq = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * VC;
+  const int tid = threadIdx.x;
+  const int cl = tid / LPC, l = tid % LPC;  // column within the CTA, lane within the column
+  const int col = col0 + cl;
+  const int dim = a.dim, vdim = a.vdim, hd = a.H * dim, hv = a.H * vdim;
+  pdl_wait();
+  const int r0 = a.cu_q[seq], n_new = a.cu_q[seq + 1] - r0;
+  if (n_new <= 0) return;
+  const bool has_prev = a.positions[r0] > 0;
+  float* state = a.state_pool + (size_t)a.state_slots[seq] * a.slot_floats + a.state_off + (size_t)head * dim * vdim;
+
+  auto load_chunk = [&](int t0, int buf) {
+    const int nt = min(TC, n_new - t0);
+    for (int i = tid; i < TC * 3 * DP; i += LR_THREADS) {
+      const int tt = i / (3 * DP), j = i % (3 * DP), part = j / DP, r = j % DP;
+      const bool ok = tt < nt && r < dim;
+      const float* src = a.qkw + (size_t)(r0 + t0 + (ok ? tt : 0)) * 3 * hd + (size_t)part * hd + head * dim + (ok ? r : 0);
+      lr_cp_async4(smem_addr(&stage[buf][tt][j]), src, ok);
+    }
+    for (int i = tid; i < TC * VC; i += LR_THREADS) {
+      const int tt = i / VC, c = i % VC;
+      const bool ok = tt < nt && col0 + c < vdim;
+      const float* src = a.vv + (size_t)(r0 + t0 + (ok ? tt : 0)) * hv + head * vdim + (ok ? col0 + c : 0);
+      lr_cp_async4(smem_addr(&stage[buf][tt][3 * DP + c]), src, ok);
+    }
+  };
+  load_chunk(0, 0);
+  cp_async_commit();
+
+  float S[RPL], U[TMIX ? RPL : 1];
+#pragma unroll
+  for (int g = 0; g < RPL / 4; g++)
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+      const int r = (g * LPC + l) * 4 + e;
+      const bool ok = r < dim && col < vdim;
+      S[g * 4 + e] = (ok && has_prev) ? state[(size_t)r * vdim + col] : 0.f;
+      if (TMIX) U[g * 4 + e] = r < dim ? a.bonus[head * dim + r] : 0.f;
+    }
+
+  const int n_chunks = (n_new + TC - 1) / TC;
+  for (int ch = 0; ch < n_chunks; ch++) {
+    const int buf = ch & 1;
+    if (ch + 1 < n_chunks) load_chunk((ch + 1) * TC, buf ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const int nt = min(TC, n_new - ch * TC);
+    for (int tt = 0; tt < nt; tt++) {
+      const float* row = stage[buf][tt];
+      const float v = row[3 * DP + cl];
+      float acc = 0.f;
+#pragma unroll
+      for (int g = 0; g < RPL / 4; g++) {
+        const int rb = (g * LPC + l) * 4;
+        const float4 q4 = *reinterpret_cast<const float4*>(row + rb);
+        const float4 k4 = *reinterpret_cast<const float4*>(row + DP + rb);
+        const float4 w4 = *reinterpret_cast<const float4*>(row + 2 * DP + rb);
+        const float qq[4] = {q4.x, q4.y, q4.z, q4.w}, kk[4] = {k4.x, k4.y, k4.z, k4.w}, ww[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+          float& s = S[g * 4 + e];
+          if (TMIX) {
+            const float kv = kk[e] * v;
+            acc = fmaf(qq[e], fmaf(U[g * 4 + e], kv, s), acc);
+            s = fmaf(ww[e], s, kv);
+          } else {
+            s = fmaf(ww[e], s, kk[e] * v);
+            acc = fmaf(qq[e], s, acc);
+          }
+        }
+      }
+#pragma unroll
+      for (int o = LPC / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (l == 0 && col < vdim) a.o[(size_t)(r0 + ch * TC + tt) * hv + head * vdim + col] = acc;
+    }
+    __syncthreads();  // the buffer is free for the load of chunk ch + 2
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int g = 0; g < RPL / 4; g++)
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+      const int r = (g * LPC + l) * 4 + e;
+      if (r < dim && col < vdim) state[(size_t)r * vdim + col] = S[g * 4 + e];
+    }
+  TRACE_EXIT(tr);
+}
+
+template <int RPL, int LPC>
+static cudaError_t linrec_scan_launch(cudaStream_t st, const LinRecArgs& a) {
+  const dim3 grid(a.n_seqs, a.H, ceil_div(a.vdim, LR_THREADS / LPC));
+  if (a.tmix) (void)launch_k(linrec_scan_kernel<RPL, LPC, true>, grid, dim3(LR_THREADS), 0, st, a, next_trace(41));
+  else (void)launch_k(linrec_scan_kernel<RPL, LPC, false>, grid, dim3(LR_THREADS), 0, st, a, next_trace(41));
+  return cudaGetLastError();
+}
+
+cudaError_t launch_linrec_scan(cudaStream_t st, const LinRecArgs& a) {
+  if (a.T <= 0 || a.n_seqs <= 0) return cudaSuccess;
+  if (a.dim > LINREC_MAX_DIM || (a.tmix && !a.bonus)) return cudaErrorInvalidValue;
+  if (a.dim <= 16) return linrec_scan_launch<4, 4>(st, a);
+  if (a.dim <= 32) return linrec_scan_launch<8, 4>(st, a);
+  if (a.dim <= 64) return linrec_scan_launch<16, 4>(st, a);
+  if (a.dim <= 128) return linrec_scan_launch<32, 4>(st, a);
+  return linrec_scan_launch<32, 8>(st, a);
+}
+
+// ------------------------------------------------------------------ gated norm of the read-out
+template <typename OT>
+__global__ void __launch_bounds__(256) linrec_out_kernel(LinRecArgs a, Trace tr) {
+  TRACE_ENTRY(tr);
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int vdim = a.vdim;
+  OT* out = (OT*)a.out + (size_t)t * a.o_ld;
+  for (int h = blockIdx.y * nw + warp; h < a.H; h += gridDim.y * nw) {
+    const float* o = a.o + (size_t)t * a.H * vdim + (size_t)h * vdim;
+    float ss = 0.f;
+    for (int i = lane; i < vdim; i += 32) ss += o[i] * o[i];
+    const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)vdim + a.eps);
+    const float* w = a.onorm_w + (size_t)h * a.onorm_ld;
+    for (int i = lane; i < vdim; i += 32) {
+      const float gt = seg_at(a.gate, t, h * vdim + i);
+      out[h * vdim + i] = from_f32<OT>(o[i] * inv * w[i] * silu(gt));
+    }
+  }
+  if (blockIdx.y == 0)
+    for (int c = a.H * vdim + threadIdx.x; c < a.o_ld; c += blockDim.x) out[c] = from_f32<OT>(0.f);
+  TRACE_EXIT(tr);
+}
+
+cudaError_t launch_linrec_out(cudaStream_t st, int odt, const LinRecArgs& a) {
+  if (a.T <= 0) return cudaSuccess;
+  const dim3 grid(a.T, a.T >= 1024 ? 1 : ceil_div(a.H, 8));
+  if (odt == DT_F32) (void)launch_k(linrec_out_kernel<float>, grid, dim3(256), 0, st, a, next_trace(42));
+  else (void)launch_k(linrec_out_kernel<bf16>, grid, dim3(256), 0, st, a, next_trace(42));
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------ token shift
+template <typename AT>
+__global__ void __launch_bounds__(256) token_shift_kernel(int T, int n_seqs, int W, int n_mix, const AT* __restrict__ h,
+                                                          const float* __restrict__ mu, const int* __restrict__ cu_q,
+                                                          const int* __restrict__ positions,
+                                                          const int* __restrict__ state_slots,
+                                                          const float* __restrict__ state_pool, size_t slot_floats,
+                                                          size_t tail_off, AT* __restrict__ out, Trace tr) {
+  TRACE_ENTRY(tr);
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int s = T == n_seqs ? t : lr_seq_of_row(cu_q, n_seqs, t);
+  const int r0 = cu_q[s];
+  const bool in_step = t > r0;
+  const bool in_slot = !in_step && positions[t] > 0;
+  const float* tail = state_pool + (size_t)state_slots[s] * slot_floats + tail_off;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float x = to_f32(h[(size_t)t * W + i]);
+    const float xp = in_step ? to_f32(h[(size_t)(t - 1) * W + i]) : (in_slot ? tail[i] : 0.f);
+    const float d = xp - x;
+    for (int m = 0; m < n_mix; m++) out[((size_t)m * T + t) * W + i] = from_f32<AT>(fmaf(d, mu[(size_t)m * W + i], x));
+  }
+  TRACE_EXIT(tr);
+}
+
+cudaError_t launch_token_shift(cudaStream_t st, int adt, int T, int n_seqs, int W, int n_mix, const void* h,
+                               const float* mu, const int* cu_q, const int* positions, const int* state_slots,
+                               const float* state_pool, size_t slot_floats, size_t tail_off, void* out) {
+  if (T <= 0) return cudaSuccess;
+  if (adt == DT_F32)
+    (void)launch_k(token_shift_kernel<float>, dim3(T), dim3(256), 0, st, T, n_seqs, W, n_mix, (const float*)h, mu, cu_q,
+                   positions, state_slots, state_pool, slot_floats, tail_off, (float*)out, next_trace(43));
+  else
+    (void)launch_k(token_shift_kernel<bf16>, dim3(T), dim3(256), 0, st, T, n_seqs, W, n_mix, (const bf16*)h, mu, cu_q,
+                   positions, state_slots, state_pool, slot_floats, tail_off, (bf16*)out, next_trace(43));
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------ tails of short convolutions
+constexpr int TAIL_MAX_JOBS = 2;
+constexpr int TAIL_MAX_TAPS = 8;
+struct TailArgs {
+  TailJob j[TAIL_MAX_JOBS];
+  int n_jobs;
+  const int *cu_q, *positions, *state_slots;
+  float* state_pool;
+  size_t slot_floats;
+};
+// grid (n_seqs, Y).  Entry i of the new tail is the input at position end - (taps - 1) + i: a row of
+// this step, an entry of the old tail, or (before the sequence's start) zero.
+template <typename AT>
+__global__ void __launch_bounds__(256) roll_tails_kernel(TailArgs a, Trace tr) {
+  TRACE_ENTRY(tr);
+  pdl_launch_dependents();
+  pdl_wait();
+  const int s = blockIdx.x;
+  const int r0 = a.cu_q[s], n_new = a.cu_q[s + 1] - r0;
+  if (n_new <= 0) return;
+  const int pos0 = a.positions[r0], end = pos0 + n_new;
+  float* slot = a.state_pool + (size_t)a.state_slots[s] * a.slot_floats;
+  for (int jb = 0; jb < a.n_jobs; jb++) {
+    const TailJob& J = a.j[jb];
+    const int keep = J.taps - 1;
+    float* tail = slot + J.tail_off;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < J.channels; c += gridDim.y * blockDim.x) {
+      float nv[TAIL_MAX_TAPS];
+#pragma unroll
+      for (int i = 0; i < TAIL_MAX_TAPS; i++) {
+        nv[i] = 0.f;
+        if (i < keep) {
+          const int p = end - keep + i;
+          if (p >= pos0) {
+            const int row = r0 + (p - pos0);
+            nv[i] = J.seg.p ? seg_at(J.seg, row, c) + (J.bias ? J.bias[c] : 0.f)
+                            : to_f32(((const AT*)J.act)[(size_t)row * J.channels + c]);
+          } else if (p >= 0) {
+            nv[i] = tail[(size_t)(p - pos0 + keep) * J.channels + c];
+          }
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < TAIL_MAX_TAPS; i++)
+        if (i < keep) tail[(size_t)i * J.channels + c] = nv[i];
+    }
+  }
+  TRACE_EXIT(tr);
+}
+
+cudaError_t launch_roll_tails(cudaStream_t st, int adt, int n_seqs, const TailJob* jobs, int n_jobs, const int* cu_q,
+                              const int* positions, const int* state_slots, float* state_pool, size_t slot_floats) {
+  if (n_seqs <= 0 || n_jobs <= 0) return cudaSuccess;
+  if (n_jobs > TAIL_MAX_JOBS) return cudaErrorInvalidValue;
+  TailArgs a{};
+  int big = 0;
+  for (int i = 0; i < n_jobs; i++) {
+    if (jobs[i].taps > TAIL_MAX_TAPS) return cudaErrorInvalidValue;
+    a.j[i] = jobs[i];
+    big = std::max(big, jobs[i].channels);
+  }
+  a.n_jobs = n_jobs; a.cu_q = cu_q; a.positions = positions; a.state_slots = state_slots;
+  a.state_pool = state_pool; a.slot_floats = slot_floats;
+  const dim3 grid(n_seqs, std::max(1, std::min(16, ceil_div(big, 256))));
+  if (adt == DT_F32) (void)launch_k(roll_tails_kernel<float>, grid, dim3(256), 0, st, a, next_trace(44));
+  else (void)launch_k(roll_tails_kernel<bf16>, grid, dim3(256), 0, st, a, next_trace(44));
+  return cudaGetLastError();
+}
+
+}  // namespace nvllm

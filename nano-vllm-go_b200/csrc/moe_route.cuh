@@ -64,19 +64,25 @@ __device__ __forceinline__ void moe_route_row(const float* y, const float* __res
   }
   __syncthreads();
   if (warp != 0) return;
-  float mx = -INFINITY;
-  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, probs[e]);
-  mx = warp_max(mx);
-  float sum = 0.f;
-  for (int e = lane; e < E; e += 32) {
-    float p = expf(probs[e] - mx);
-    probs[e] = p;
-    sum += p;
+  if (ro.sigmoid) {
+    // every expert scores on its own
+    for (int e = lane; e < E; e += 32) probs[e] = 1.0f / (1.0f + expf(-probs[e]));
+    __syncwarp();
+  } else {
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, probs[e]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) {
+      float p = expf(probs[e] - mx);
+      probs[e] = p;
+      sum += p;
+    }
+    sum = warp_sum(sum);
+    __syncwarp();
+    for (int e = lane; e < E; e += 32) probs[e] = probs[e] / sum;
+    __syncwarp();
   }
-  sum = warp_sum(sum);
-  __syncwarp();
-  for (int e = lane; e < E; e += 32) probs[e] = probs[e] / sum;
-  __syncwarp();
   // group-limited choice: a group scores as its best expert; group g stays iff fewer than
   // `keep` groups beat it (higher score, or equal score and lower index).  Experts of the other
   // groups are taken out of the selection below (their probabilities are not needed again).
@@ -127,7 +133,8 @@ __device__ __forceinline__ void moe_route_row(const float* y, const float* __res
   }
   if (lane < k) {
     topk_idx[t * k + lane] = sel_i;
-    topk_w[t * k + lane] = ro.raw ? sel_p * ro.scale : sel_p / ksum;
+    const float wgt = ro.raw ? sel_p * ro.scale : sel_p / ksum;
+    topk_w[t * k + lane] = ro.square ? wgt * wgt : wgt;
   }
 }
 
