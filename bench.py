@@ -547,6 +547,74 @@ def hybrid_1b():
     return replace(cfg, name="hybrid-mamba2-1b")
 
 
+def lazovik_cfg(width, n_layers, vocab, every, g_heads, g_dim, g_vdim, a_heads, a_kv, a_dim, conv, chunk, t_heads, t_dim,
+                rank, experts, top, ff, shared, loop=None):
+    """Gated-linear-attention layers with every `every`-th layer an attention + time-mixing layer;
+    every layer with the mixture of squared-ReLU experts.  loop = (start, stop, times)."""
+    layers = []
+    moe = dict(mlp=C.MLP_MOE, act=C.FFN_RELU2, ff=ff, experts=experts, top=top, route_sigmoid=1, weight_on_input=1,
+               shared_ff=shared)
+    for l in range(n_layers):
+        if l % every == every - 1:
+            kw = dict(mixer=C.MIXER_ATTN_TMIX, heads=a_heads, kv_heads=a_kv, dim=a_dim, vdim=a_dim, conv=conv, chunk=chunk,
+                      scale=float(a_dim ** -0.5), softcap=30.0, qk_norm=2, proj_bias=1, out_gate=1, rot_dims=a_dim // 2,
+                      rot_base=500000.0, rot_factor=8.0, rot_original=8192.0, rot_fast=32.0, rot_slow=1.0,
+                      heads2=t_heads, dim2=t_dim, lowrank=rank, mix_scale=1.0, mix2_scale=1.0)
+        else:
+            kw = dict(mixer=C.MIXER_GLA, heads=g_heads, dim=g_dim, vdim=g_vdim, tau=16.0, lowrank=rank)
+        layers.append(C.LayerSpec(**kw, **moe))
+    lp = loop or (0, 0, 1)
+    return C.ListedModelConfig("lazovik", vocab, width, tuple(layers), 1e-5, arch=C.ARCH_LAZOVIK,
+                               block_style=C.LBLOCK_SEQUENTIAL_PRENORM, loop_start=lp[0], loop_stop=lp[1], loop_times=lp[2])
+
+
+def lazovik_device_weights(cfg, device, seed=1234):
+    import torch
+    g = torch.Generator(device=f"cuda:{device}")
+    for i, (name, shape) in enumerate(cfg.tensor_shapes().items()):
+        g.manual_seed(seed * 1000003 + i)
+        t = torch.empty(shape, dtype=torch.float32, device=f"cuda:{device}")
+        if name.endswith("a2.b"):
+            t.uniform_(0.0, 4.0, generator=g)       # decays near one
+        elif name.endswith(".w0"):
+            t.uniform_(-5.0, -0.5, generator=g)
+        elif ".mu." in name:
+            t.uniform_(0.0, 1.0, generator=g)
+        elif name.endswith(".b"):
+            t.normal_(0.0, 0.02, generator=g)
+        elif len(shape) == 1:
+            t.normal_(1.0, 0.02, generator=g)       # norm weights
+        elif name.endswith(".conv"):
+            t.normal_(0.0, shape[1] ** -0.5, generator=g)
+        elif name.endswith(".down"):
+            t.normal_(0.0, 0.3 * shape[1] ** -0.5, generator=g)
+        else:
+            t.normal_(0.0, 0.02 if name in ("embed", "loop.step") else shape[1] ** -0.5, generator=g)
+        yield name, t.to(torch.bfloat16).view(torch.int16).cpu().numpy().view(np.uint16)
+        del t
+
+
+# width 1024, 24 layer executions like Granite-MoE-1B: gated linear attention (8 heads, 64 x 128 state each) with
+# every fourth layer attention (16 heads of 64 over 4 K / V heads, 4 taps, chunks of 1024) + time mixing (8 heads of
+# 64 x 64); 32 experts of 768 (two matrices: the parameters of Granite's three of 512), 8 per token, an always-on
+# expert of 1024.  lz-1b-loop: 12 layers run twice.
+def _lz(n_layers, loop=None):
+    return lambda: lazovik_cfg(1024, n_layers, 49155, 4, 8, 64, 128, 16, 4, 64, 4, 1024, 8, 64, 64, 32, 8, 768, 1024, loop)
+
+
+LAZOVIK_SIZES = {
+    "lz-1b": (_lz(24), "granite-moe-1b", 128, 128, 128),
+    "lz-1b-long": (_lz(24), "granite-moe-1b", 16, 4096, 64),
+    "lz-1b-loop": (_lz(12, (0, 12, 2)), "granite-moe-1b", 64, 512, 128),
+}
+
+
+def zozonex_moe_width():
+    """The delta-rule / window-attention design at the width and depth of the sizes above: the
+    library's other layer-listed model with a recurrent scan and a windowed attention."""
+    return zozonex_cfg(1024, 24, 49155, 8, 8, 64, 128, 4, 16, 4, 64, 1024, 4096)
+
+
 DESIGN_SIZES = {
     # name: (layer-listed config, closest uniform preset, batch, prompt, decode steps)
     "dense-1b": (lambda: dugopel_cfg(2048, 16, 32, 64, 32, 64, 128, 768, 8192, 128256), "llama-3.2-1b", 64, 512, 128),
@@ -569,8 +637,8 @@ def design_bench(args):
     peaks = load_peaks()
     R = nvllm_pkg.sub("runner")
     design = args.design
-    sizes = ZOZONEX_SIZES if design == "zozonex" else DESIGN_SIZES
-    gen = zozonex_device_weights if design == "zozonex" else dugopel_device_weights
+    sizes = {"zozonex": ZOZONEX_SIZES, "lazovik": LAZOVIK_SIZES}.get(design, DESIGN_SIZES)
+    gen = {"zozonex": zozonex_device_weights, "lazovik": lazovik_device_weights}.get(design, dugopel_device_weights)
     out = {"design": design, "dtype": "bf16", "data": "synthetic (random-init weights, random prompts)",
            "steps": args.steps, "warmup": args.warmup, "peaks": peaks, "sizes": {}}
     names = [n for n in sizes if args.design_size in (None, n)]
@@ -578,14 +646,18 @@ def design_bench(args):
         mk, base_name, batch, P, D = sizes[name]
         entry = {"batch": batch, "prompt_len": P, "decode_steps": D}
         others = (base_name, "hybrid-mamba2-1b") if design == "zozonex" and not args.no_hybrid else (base_name,)
+        if design == "lazovik" and not args.no_hybrid:
+            others = (base_name, "zozonex-1b")
         for which in (design,) + others:
-            cfg = mk() if which == design else hybrid_1b() if which == "hybrid-mamba2-1b" else C.PRESETS[base_name]()
-            if which != design and cfg.max_seq_len < P + D + 1:
+            cfg = mk() if which == design else hybrid_1b() if which == "hybrid-mamba2-1b" else \
+                zozonex_moe_width() if which == "zozonex-1b" else C.PRESETS[base_name]()
+            if which != design and hasattr(cfg, "max_seq_len") and cfg.max_seq_len < P + D + 1:
                 from dataclasses import replace
                 cfg = replace(cfg, max_seq_len=P + D + 32)
             job = Job(cfg, batch, P, D, 4321)
-            if which == design:
-                run = R.CudaModelRunner(cfg, gen(cfg, device), precision=C.PREC_BF16,
+            if which == design or which == "zozonex-1b":
+                wgen = gen if which == design else zozonex_device_weights
+                run = R.CudaModelRunner(cfg, wgen(cfg, device), precision=C.PREC_BF16,
                                         num_kv_blocks=job.num_blocks, device=device, max_num_seqs=job.n,
                                         max_batched_tokens=batch * P, sampling=None, num_state_slots=job.n)
                 if run.needs_state_slots:
@@ -670,11 +742,12 @@ def main():
     ap.add_argument("--no-profile", action="store_true")
     ap.add_argument("--no-tp", action="store_true",
                     help="skip the Falcon-7B tensor-parallel leg (configs[3] at tp = --gpus)")
-    ap.add_argument("--design", default=None, choices=["dugopel", "zozonex"],
+    ap.add_argument("--design", default=None, choices=["dugopel", "zozonex", "lazovik"],
                     help="instead of the default workload: the layer-listed design beside the closest "
                          "uniform model at equal size (prefill and decode, per-kernel roofline)")
-    ap.add_argument("--no-hybrid", action="store_true", help="--design zozonex: skip the Mamba2 hybrid baseline")
-    ap.add_argument("--design-size", default=None, choices=sorted(DESIGN_SIZES) + sorted(ZOZONEX_SIZES))
+    ap.add_argument("--no-hybrid", action="store_true",
+                    help="--design zozonex / lazovik: skip the second baseline (Mamba2 hybrid / Zozonex at equal width)")
+    ap.add_argument("--design-size", default=None, choices=sorted(DESIGN_SIZES) + sorted(ZOZONEX_SIZES) + sorted(LAZOVIK_SIZES))
     args = ap.parse_args()
     if args.design:
         return design_bench(args)

@@ -8,8 +8,8 @@
 // key entries.  The read-out of a head is divided by its root mean square, multiplied by a weight
 // and by silu(gate) and goes to the output projection.
 //
-//   linrec_prep_kernel   per token: split-K sums of the projections, q scaled, the second step of
-//                        the decay's projection (fp32 FMA, rank is small) and the decay itself —
+//   linrec_prep_kernel   per tile of tokens: split-K sums of the projections, q scaled, the second step of
+//                        the decay's projection (fp32 FMA, the inner size is small) and the decay itself —
 //                        logarithms, exponentials and sigmoids in fp32 (log-sigmoid form, no overflow).
 //   linrec_scan_kernel   CTA = (sequence, head, 128 / LPC value columns).  A column of the state is
 //                        independent of the others: it lives in the registers of LPC lanes
@@ -56,48 +56,105 @@ __device__ __forceinline__ void lr_cp_async4(uint32_t dst, const void* src, bool
 }  // namespace
 
 // ------------------------------------------------------------------ projections' epilogue
-// grid (T, Y), 256 threads; channel c of the H * dim key entries: q, k, decay; then the values.
+// grid (ceil(T / TT), Y), 256 threads: a CTA takes TT tokens, a thread one of the H * dim key
+// entries at a time.  The entry's row of the decay's second-step matrix is read once (16 floats
+// at a time, in registers) for all TT tokens, whose inner vectors sit in shared memory and are
+// read as broadcasts — the matrix crosses L2 once per TT tokens instead of once per token.
+constexpr int LP_RC = 16;  // inner entries per register chunk
+
+template <int TT>
 __global__ void __launch_bounds__(256) linrec_prep_kernel(LinRecArgs a, Trace tr) {
   TRACE_ENTRY(tr);
   pdl_launch_dependents();
-  extern __shared__ float lr[];  // [rank]
+  extern __shared__ __align__(16) float lr[];  // [TT][rank_p], rank_p = rank rounded up to LP_RC, zero padded
   pdl_wait();
-  const int t = blockIdx.x;
+  const int t0 = blockIdx.x * TT;
+  const int nt = min(TT, a.T - t0);
+  const int rank_p = (a.rank + LP_RC - 1) / LP_RC * LP_RC;
   const int hd = a.H * a.dim, hv = a.H * a.vdim;
-  for (int r = threadIdx.x; r < a.rank; r += blockDim.x) {
-    const float x = seg_at(a.lr, t, r);
-    lr[r] = a.tmix ? tanhf(x) : x;
+  for (int i = threadIdx.x; i < TT * rank_p; i += blockDim.x) {
+    const int tt = i / rank_p, r = i % rank_p;
+    float x = 0.f;
+    if (tt < nt && r < a.rank) {
+      x = seg_at(a.lr, t0 + tt, r);
+      if (a.tmix) x = tanhf(x);
+    }
+    lr[i] = x;
   }
   __syncthreads();
-  float* qkw = a.qkw + (size_t)t * 3 * hd;
   const float inv_tau = 1.0f / a.tau;
+  const bool vec_ok = (a.rank % 4) == 0;
   for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < hd; c += gridDim.y * blockDim.x) {
     const float* w = a.w2 + (size_t)c * a.rank;
-    float z = 0.f;
-    for (int r = 0; r < a.rank; r++) z = fmaf(w[r], lr[r], z);
-    z += a.w2b[c];
-    float decay;
-    if (a.tmix) {
-      decay = expf(-expf(z));
-    } else {
-      // sigmoid(z)^(1 / tau) = exp(log sigmoid(z) / tau), log sigmoid(z) = min(z, 0) - log1p(exp(-|z|))
-      const float ls = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
-      decay = expf(ls * inv_tau);
+    float z[TT];
+#pragma unroll
+    for (int tt = 0; tt < TT; tt++) z[tt] = 0.f;
+    for (int r0 = 0; r0 < a.rank; r0 += LP_RC) {
+      float wr[LP_RC];
+      if (vec_ok && r0 + LP_RC <= a.rank) {
+#pragma unroll
+        for (int q = 0; q < LP_RC / 4; q++) {
+          const float4 v = *reinterpret_cast<const float4*>(w + r0 + 4 * q);
+          wr[4 * q] = v.x; wr[4 * q + 1] = v.y; wr[4 * q + 2] = v.z; wr[4 * q + 3] = v.w;
+        }
+      } else {
+#pragma unroll
+        for (int q = 0; q < LP_RC; q++) wr[q] = r0 + q < a.rank ? w[r0 + q] : 0.f;
+      }
+#pragma unroll
+      for (int tt = 0; tt < TT; tt++) {
+        const float* l = lr + tt * rank_p + r0;
+#pragma unroll
+        for (int q = 0; q < LP_RC / 4; q++) {
+          const float4 v = *reinterpret_cast<const float4*>(l + 4 * q);
+          z[tt] = fmaf(wr[4 * q], v.x, z[tt]);
+          z[tt] = fmaf(wr[4 * q + 1], v.y, z[tt]);
+          z[tt] = fmaf(wr[4 * q + 2], v.z, z[tt]);
+          z[tt] = fmaf(wr[4 * q + 3], v.w, z[tt]);
+        }
+      }
     }
-    qkw[c] = seg_at(a.q, t, c) * a.qmul;
-    qkw[hd + c] = seg_at(a.k, t, c);
-    qkw[2 * hd + c] = decay;
+    const float b = a.w2b[c];
+#pragma unroll
+    for (int tt = 0; tt < TT; tt++) {
+      if (tt >= nt) break;
+      const float zz = z[tt] + b;
+      float decay;
+      if (a.tmix) {
+        decay = expf(-expf(zz));
+      } else {
+        // sigmoid(z)^(1 / tau) = exp(log sigmoid(z) / tau), log sigmoid(z) = min(z, 0) - log1p(exp(-|z|))
+        const float ls = fminf(zz, 0.f) - log1pf(expf(-fabsf(zz)));
+        decay = expf(ls * inv_tau);
+      }
+      float* qkw = a.qkw + (size_t)(t0 + tt) * 3 * hd;
+      qkw[c] = seg_at(a.q, t0 + tt, c) * a.qmul;
+      qkw[hd + c] = seg_at(a.k, t0 + tt, c);
+      qkw[2 * hd + c] = decay;
+    }
   }
-  float* vv = a.vv + (size_t)t * hv;
-  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < hv; c += gridDim.y * blockDim.x) vv[c] = seg_at(a.v, t, c);
+  for (int tt = 0; tt < nt; tt++) {
+    float* vv = a.vv + (size_t)(t0 + tt) * hv;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < hv; c += gridDim.y * blockDim.x) vv[c] = seg_at(a.v, t0 + tt, c);
+  }
   TRACE_EXIT(tr);
 }
 
 cudaError_t launch_linrec_prep(cudaStream_t st, const LinRecArgs& a) {
   if (a.T <= 0) return cudaSuccess;
   const int big = std::max(a.H * a.dim, a.H * a.vdim);
-  const dim3 grid(a.T, a.T >= 1024 ? 1 : std::min(8, ceil_div(big, 256)));
-  (void)launch_k(linrec_prep_kernel, grid, dim3(256), (size_t)a.rank * sizeof(float), st, a, next_trace(40));
+  const int rank_p = (a.rank + LP_RC - 1) / LP_RC * LP_RC;
+  if (a.T >= 2048) {
+    const size_t smem = (size_t)16 * rank_p * sizeof(float);
+    if (smem > 48 * 1024) cudaFuncSetAttribute(linrec_prep_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    (void)launch_k(linrec_prep_kernel<16>, dim3(ceil_div(a.T, 16), std::min(4, ceil_div(big, 256))), dim3(256), smem, st, a,
+                   next_trace(40));
+  } else {
+    const size_t smem = (size_t)4 * rank_p * sizeof(float);
+    if (smem > 48 * 1024) cudaFuncSetAttribute(linrec_prep_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    (void)launch_k(linrec_prep_kernel<4>, dim3(ceil_div(a.T, 4), std::min(8, ceil_div(big, 256))), dim3(256), smem, st, a,
+                   next_trace(40));
+  }
   return cudaGetLastError();
 }
 
