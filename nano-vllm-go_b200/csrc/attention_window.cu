@@ -41,9 +41,16 @@ __device__ __forceinline__ int first_key(const WinAttnArgs& a, int i) {
   if (a.chunk > 0) return i / a.chunk * a.chunk;
   return a.window > 0 ? max(0, i - a.window + 1) : 0;
 }
-// cap * tanh(s / cap), the library tanh: a score is small beside the cap more often than not, and
-// there a tanh built on a fast exponential loses the digits that fp32 scores are asked to keep
-__device__ __forceinline__ float cap_score(float s, float cap) { return cap * tanhf(s / cap); }
+// cap * tanh(s / cap).  FAST (the bf16 kernels): tanh through one fast exponential and one fast
+// division; its ABSOLUTE error is about cap * 3e-7 (the exponential's 2 ulp), which is what a
+// softmax weight sees, far below the bf16 rounding of the weights.  Otherwise the library tanh.
+template <bool FAST>
+__device__ __forceinline__ float cap_score(float s, float cap) {
+  if (!FAST) return cap * tanhf(s / cap);
+  const float x = __fdividef(s, cap);
+  const float e = __expf(-2.0f * fabsf(x));
+  return copysignf(cap * __fdividef(1.0f - e, 1.0f + e), x);
+}
 __device__ __forceinline__ float sum_slices(const float* __restrict__ p, int S, size_t stride) {
   float acc = 0.f;
   for (int s = 0; s < S; s++) acc += p[(size_t)s * stride];
@@ -148,7 +155,7 @@ cudaError_t launch_winattn_prep(cudaStream_t st, int qdt, int kvdt, const WinAtt
 // staged in shared memory with their sums of squares, v straight into the pool, the gates'
 // sigmoids out.  Pass 2: the two whole-row norms, weights, rotation, Q and K out.
 template <typename QT, typename KT>
-__global__ void __launch_bounds__(256) winattn_prep_conv_kernel(WinAttnArgs a, ConvAttnPrep c, Trace tr) {
+__global__ void __launch_bounds__(1024) winattn_prep_conv_kernel(WinAttnArgs a, ConvAttnPrep c, Trace tr) {
   TRACE_ENTRY(tr);
   pdl_launch_dependents();
   extern __shared__ float qk[];  // [n_q + n_k] convolved
@@ -173,17 +180,36 @@ __global__ void __launch_bounds__(256) winattn_prep_conv_kernel(WinAttnArgs a, C
   const float* tail = c.state_pool + (size_t)c.state_slots[s] * c.slot_floats + c.tail_off;
   const int slot = a.slots[t];
   const int blk = slot / KV_BLOCK, off = slot % KV_BLOCK;
+  // where tap j's input lives is the same for every channel of the row: a row of this step's
+  // partials, a row of the slot's tail, or nowhere (before the sequence's start)
+  const float* src[8];
+  bool from_step[8];
+#pragma unroll
+  for (int j = 0; j < 8; j++) {
+    src[j] = nullptr;
+    from_step[j] = false;
+    if (j < c.taps) {
+      const int back = keep - j;  // input `back` positions before this token
+      if (back <= li) { src[j] = a.in_p + (size_t)(t - back) * a.in_ld; from_step[j] = true; }
+      else if (back <= pos) src[j] = tail + (size_t)(keep - (back - li)) * n_ch;
+    }
+  }
   float ssq = 0.f, ssk = 0.f;
   for (int ch = threadIdx.x; ch < n_ch; ch += blockDim.x) {
     const float b = c.bias ? c.bias[ch] : 0.f;
-    float y = 0.f;
-    for (int j = 0; j < c.taps; j++) {
-      const int back = keep - j;  // input `back` positions before this token
-      float u = 0.f;
-      if (back <= li) u = sum_slices(a.in_p + (size_t)(t - back) * a.in_ld + ch, a.in_S, a.in_stride) + b;
-      else if (back <= pos) u = tail[(size_t)(keep - (back - li)) * n_ch + ch];
-      y = fmaf(c.conv_w[(size_t)ch * c.taps + j], u, y);
+    float u[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) {  // all the taps' loads first
+      u[j] = 0.f;
+      if (j < c.taps && src[j]) {
+        if (a.in_S == 1) u[j] = src[j][ch] + (from_step[j] ? b : 0.f);  // one slice: nothing to sum, no loop around the load
+        else u[j] = from_step[j] ? sum_slices(src[j] + ch, a.in_S, a.in_stride) + b : src[j][ch];
+      }
     }
+    float y = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; j++)
+      if (j < c.taps) y = fmaf(c.conv_w[(size_t)ch * c.taps + j], u[j], y);
     if (ch < n_q) { qk[ch] = y; ssq += y * y; }
     else if (ch < n_q + n_k) { qk[ch] = y; ssk += y * y; }
     else {
@@ -225,14 +251,16 @@ __global__ void __launch_bounds__(256) winattn_prep_conv_kernel(WinAttnArgs a, C
 
 cudaError_t launch_winattn_prep_conv(cudaStream_t st, int qdt, int kvdt, const WinAttnArgs& a, const ConvAttnPrep& c) {
   if (a.T <= 0) return cudaSuccess;
-  if (c.taps < 1 || 2 * c.rot_half > a.dim || !a.own_kv) return cudaErrorInvalidValue;
+  if (c.taps < 1 || c.taps > 8 || 2 * c.rot_half > a.dim || !a.own_kv) return cudaErrorInvalidValue;
   const size_t smem = (size_t)(a.H + a.G) * a.dim * sizeof(float);
+  // few rows (decode): the row's channels spread over more threads
+  const dim3 block(a.T >= 1024 ? 256 : 1024);
   if (qdt == DT_F32 && kvdt == DT_F32) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(winattn_prep_conv_kernel<float, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    (void)launch_k(winattn_prep_conv_kernel<float, float>, dim3(a.T), dim3(256), smem, st, a, c, next_trace(38));
+    (void)launch_k(winattn_prep_conv_kernel<float, float>, dim3(a.T), block, smem, st, a, c, next_trace(38));
   } else if (qdt == DT_BF16 && kvdt == DT_BF16) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(winattn_prep_conv_kernel<bf16, bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    (void)launch_k(winattn_prep_conv_kernel<bf16, bf16>, dim3(a.T), dim3(256), smem, st, a, c, next_trace(38));
+    (void)launch_k(winattn_prep_conv_kernel<bf16, bf16>, dim3(a.T), block, smem, st, a, c, next_trace(38));
   } else {
     return cudaErrorInvalidValue;
   }
@@ -317,7 +345,7 @@ __global__ void __launch_bounds__(256) winattn_kernel(WinAttnArgs a, Trace tr) {
           const float* kr = Ks + lane * kld;
           float d = 0.f;
           for (int i = 0; i < dim; i++) d = fmaf(qr[i], kr[i], d);
-          s = a.softcap > 0.f ? cap_score(d, a.softcap) : d;
+          s = a.softcap > 0.f ? cap_score<sizeof(QT) == 2>(d, a.softcap) : d;
         }
         const float cmax = warp_max(s);
         if (cmax == -INFINITY) continue;  // no key of this tile is visible to the query
@@ -417,7 +445,7 @@ __global__ void __launch_bounds__(128) winattn_decode_kernel(WinAttnArgs a, Trac
       const KT* kr = kpool + (((size_t)bt[j / KV_BLOCK] * a.G + g) * KV_BLOCK + (j % KV_BLOCK)) * dim;
       float d = 0.f;
       for (int i = 0; i < dim; i++) d = fmaf(qs[i], to_f32(kr[i]), d);
-      s = a.softcap > 0.f ? cap_score(d, a.softcap) : d;
+      s = a.softcap > 0.f ? cap_score<sizeof(QT) == 2>(d, a.softcap) : d;
     }
     const float mn = fmaxf(m, warp_max(s));  // lane 0 of the chunk is always visible
     const float corr = (m == -INFINITY) ? 0.f : expf(m - mn);
@@ -568,7 +596,7 @@ __global__ void __launch_bounds__(256, (GQMAX * VPT <= 16) ? 2 : 1) winattn_deco
     float p[GQMAX];
 #pragma unroll
     for (int q = 0; q < GQMAX; q++) {
-      const float sv = vis ? (a.softcap > 0.f ? cap_score(s[q], a.softcap) : s[q]) : -INFINITY;
+      const float sv = vis ? (a.softcap > 0.f ? cap_score<sizeof(QT) == 2>(s[q], a.softcap) : s[q]) : -INFINITY;
       const float mn = fmaxf(m[q], warp_max(sv));  // lane 0 of a chunk is always visible
       const float corr = (m[q] == -INFINITY) ? 0.f : expf(m[q] - mn);
       p[q] = vis ? expf(sv - mn) : 0.f;
@@ -803,7 +831,7 @@ __global__ void __launch_bounds__(128) winattn_mma_kernel(WinAttnArgs a, Trace t
 #pragma unroll
         for (int nb = 0; nb < WM_K / 8; nb++)
 #pragma unroll
-          for (int e = 0; e < 4; e++) s[nb][e] = cap_score(s[nb][e] * a.scale, a.softcap) * (1.4426950408889634f / sc);
+          for (int e = 0; e < 4; e++) s[nb][e] = cap_score<true>(s[nb][e] * a.scale, a.softcap) * (1.4426950408889634f / sc);
       }
       if (interior) {
 #pragma unroll
@@ -998,7 +1026,7 @@ __global__ void __launch_bounds__(128) winattn_decode_mma_kernel(WinAttnArgs a, 
 #pragma unroll
         for (int e = 0; e < 4; e++) {
           const int j = j0 + nb * 8 + tig * 2 + (e & 1);
-          const float sv = a.softcap > 0.f ? cap_score(s[nb][e] * a.scale, a.softcap) * 1.4426950408889634f : s[nb][e] * sc;
+          const float sv = a.softcap > 0.f ? cap_score<true>(s[nb][e] * a.scale, a.softcap) * 1.4426950408889634f : s[nb][e] * sc;
           const float v = (j >= k_lo && j <= qp) ? sv : -INFINITY;  // every row sits at position qp
           s[nb][e] = v;
           if (e & 2) mx_hi = fmaxf(mx_hi, v);

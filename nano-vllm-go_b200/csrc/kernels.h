@@ -500,7 +500,7 @@ struct LinRecArgs {
   int T, n_seqs;
   int H, dim, vdim;
   int tmix;              // 0: gated linear attention, 1: time mixing (read before the update, bonus u)
-  float eps, tau, qmul;  // q <- q * qmul; gated linear attention: decay = sigmoid(z)^(1 / tau)
+  float eps, tau, qmul;  // read-outs times qmul (= q scaled); gated linear attention: decay = sigmoid(z)^(1 / tau)
   LinSeg q, k, v, lr, gate;  // lr [T, rank]: inner result of the decay's two-step projection
   int rank;
   const float* w2;       // [H dim, rank] fp32; z = w2 f(lr) + w2b, f = tanh for time mixing

@@ -11,8 +11,9 @@
 //   linrec_prep_kernel   per tile of tokens: split-K sums of the projections, q scaled, the second step of
 //                        the decay's projection (fp32 FMA, the inner size is small) and the decay itself —
 //                        logarithms, exponentials and sigmoids in fp32 (log-sigmoid form, no overflow).
-//   linrec_scan_kernel   CTA = (sequence, head, 128 / LPC value columns).  A column of the state is
-//                        independent of the others: it lives in the registers of LPC lanes
+//   linrec_scan_kernel   CTA = (sequence, head, CC * 128 / LPC value columns).  A column of the state is
+//                        independent of the others: it lives in the registers of LPC lanes (a lane holds
+//                        its rows of CC columns, so a row's q / k / decay is read once for CC updates)
 //                        (RPL rows each, rows dealt in groups of four so that the lanes' 16-byte
 //                        shared-memory reads of q / k / decay do not collide); per token one
 //                        pass over the rows and log2(LPC) shuffles.  Token inputs are staged
@@ -49,6 +50,9 @@ __device__ __forceinline__ float seg_at(const LinSeg& g, int t, int c) {
   for (int s = 0; s < g.S; s++) acc += p[(size_t)s * g.stride];
   return acc;
 }
+// q, k and v projections that came out as one slice each need no summing: the scan reads them
+// where the GEMMs left them and the prep kernel writes only the decay
+__host__ __device__ __forceinline__ bool linrec_direct(const LinRecArgs& a) { return a.q.S == 1 && a.k.S == 1 && a.v.S == 1; }
 __device__ __forceinline__ void lr_cp_async4(uint32_t dst, const void* src, bool ok) {
   const int n = ok ? 4 : 0;  // src-size 0: the destination is filled with zeros
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
@@ -57,7 +61,7 @@ __device__ __forceinline__ void lr_cp_async4(uint32_t dst, const void* src, bool
 
 // ------------------------------------------------------------------ projections' epilogue
 // grid (ceil(T / TT), Y), 256 threads: a CTA takes TT tokens, a thread one of the H * dim key
-// entries at a time.  The entry's row of the decay's second-step matrix is read once (16 floats
+// entries at a time.  Output: qkw rows [q | k | decay] and vv (q unscaled: the scan scales its read-outs).  The entry's row of the decay's second-step matrix is read once (16 floats
 // at a time, in registers) for all TT tokens, whose inner vectors sit in shared memory and are
 // read as broadcasts — the matrix crosses L2 once per TT tokens instead of once per token.
 constexpr int LP_RC = 16;  // inner entries per register chunk
@@ -84,6 +88,7 @@ __global__ void __launch_bounds__(256) linrec_prep_kernel(LinRecArgs a, Trace tr
   __syncthreads();
   const float inv_tau = 1.0f / a.tau;
   const bool vec_ok = (a.rank % 4) == 0;
+  const bool direct = linrec_direct(a);
   for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < hd; c += gridDim.y * blockDim.x) {
     const float* w = a.w2 + (size_t)c * a.rank;
     float z[TT];
@@ -115,6 +120,15 @@ __global__ void __launch_bounds__(256) linrec_prep_kernel(LinRecArgs a, Trace tr
       }
     }
     const float b = a.w2b[c];
+    float qv[TT], kv[TT];
+    if (!direct) {  // all the loads first
+#pragma unroll
+      for (int tt = 0; tt < TT; tt++)
+        if (tt < nt) {
+          qv[tt] = seg_at(a.q, t0 + tt, c);
+          kv[tt] = seg_at(a.k, t0 + tt, c);
+        }
+    }
 #pragma unroll
     for (int tt = 0; tt < TT; tt++) {
       if (tt >= nt) break;
@@ -128,11 +142,14 @@ __global__ void __launch_bounds__(256) linrec_prep_kernel(LinRecArgs a, Trace tr
         decay = expf(ls * inv_tau);
       }
       float* qkw = a.qkw + (size_t)(t0 + tt) * 3 * hd;
-      qkw[c] = seg_at(a.q, t0 + tt, c) * a.qmul;
-      qkw[hd + c] = seg_at(a.k, t0 + tt, c);
+      if (!direct) {
+        qkw[c] = qv[tt];
+        qkw[hd + c] = kv[tt];
+      }
       qkw[2 * hd + c] = decay;
     }
   }
+  if (direct) return;
   for (int tt = 0; tt < nt; tt++) {
     float* vv = a.vv + (size_t)(t0 + tt) * hv;
     for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < hv; c += gridDim.y * blockDim.x) vv[c] = seg_at(a.v, t0 + tt, c);
@@ -161,19 +178,20 @@ cudaError_t launch_linrec_prep(cudaStream_t st, const LinRecArgs& a) {
 // ------------------------------------------------------------------ scan over tokens
 constexpr int LR_THREADS = 128;
 
-template <int RPL, int LPC, bool TMIX>
+// CC: value columns per thread (the q / k / decay reads of a row are shared by them)
+template <int RPL, int LPC, int CC, bool TMIX>
 __global__ void __launch_bounds__(LR_THREADS) linrec_scan_kernel(LinRecArgs a, Trace tr) {
   TRACE_ENTRY(tr);
   pdl_launch_dependents();
-  constexpr int DP = RPL * LPC;          // rows of the state, padded
-  constexpr int VC = LR_THREADS / LPC;   // value columns of this CTA
+  constexpr int DP = RPL * LPC;           // rows of the state, padded
+  constexpr int CG = LR_THREADS / LPC;    // column groups = threads along the columns
+  constexpr int VC = CG * CC;             // value columns of this CTA
   constexpr int TC = DP >= 256 ? 4 : (DP >= 128 ? 8 : 16);  // tokens per staged chunk
-  constexpr int ROW = 3 * DP + VC;       // floats of one staged token: q | k | decay | v
+  constexpr int ROW = 3 * DP + VC;        // floats of one staged token: q | k | decay | v
   __shared__ __align__(16) float stage[2][TC][ROW];
   const int seq = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * VC;
   const int tid = threadIdx.x;
-  const int cl = tid / LPC, l = tid % LPC;  // column within the CTA, lane within the column
-  const int col = col0 + cl;
+  const int cl = tid / LPC, l = tid % LPC;  // column group, lane within the column
   const int dim = a.dim, vdim = a.vdim, hd = a.H * dim, hv = a.H * vdim;
   pdl_wait();
   const int r0 = a.cu_q[seq], n_new = a.cu_q[seq + 1] - r0;
@@ -181,32 +199,41 @@ __global__ void __launch_bounds__(LR_THREADS) linrec_scan_kernel(LinRecArgs a, T
   const bool has_prev = a.positions[r0] > 0;
   float* state = a.state_pool + (size_t)a.state_slots[seq] * a.slot_floats + a.state_off + (size_t)head * dim * vdim;
 
+  // q | k | decay | v of the step's rows: the projections' own output when it needs no summing
+  const bool direct = linrec_direct(a);
+  const float* part_p[3] = {direct ? a.q.p : a.qkw, direct ? a.k.p : a.qkw + hd, a.qkw + 2 * hd};
+  const size_t part_ld[3] = {direct ? (size_t)a.q.ld : (size_t)3 * hd, direct ? (size_t)a.k.ld : (size_t)3 * hd, (size_t)3 * hd};
+  const float* v_p = direct ? a.v.p : a.vv;
+  const size_t v_ld = direct ? (size_t)a.v.ld : (size_t)hv;
   auto load_chunk = [&](int t0, int buf) {
     const int nt = min(TC, n_new - t0);
     for (int i = tid; i < TC * 3 * DP; i += LR_THREADS) {
       const int tt = i / (3 * DP), j = i % (3 * DP), part = j / DP, r = j % DP;
       const bool ok = tt < nt && r < dim;
-      const float* src = a.qkw + (size_t)(r0 + t0 + (ok ? tt : 0)) * 3 * hd + (size_t)part * hd + head * dim + (ok ? r : 0);
+      const float* src = part_p[part] + (size_t)(r0 + t0 + (ok ? tt : 0)) * part_ld[part] + head * dim + (ok ? r : 0);
       lr_cp_async4(smem_addr(&stage[buf][tt][j]), src, ok);
     }
     for (int i = tid; i < TC * VC; i += LR_THREADS) {
       const int tt = i / VC, c = i % VC;
       const bool ok = tt < nt && col0 + c < vdim;
-      const float* src = a.vv + (size_t)(r0 + t0 + (ok ? tt : 0)) * hv + head * vdim + (ok ? col0 + c : 0);
+      const float* src = v_p + (size_t)(r0 + t0 + (ok ? tt : 0)) * v_ld + head * vdim + (ok ? col0 + c : 0);
       lr_cp_async4(smem_addr(&stage[buf][tt][3 * DP + c]), src, ok);
     }
   };
   load_chunk(0, 0);
   cp_async_commit();
 
-  float S[RPL], U[TMIX ? RPL : 1];
+  float S[CC][RPL], U[TMIX ? RPL : 1];
 #pragma unroll
   for (int g = 0; g < RPL / 4; g++)
 #pragma unroll
     for (int e = 0; e < 4; e++) {
       const int r = (g * LPC + l) * 4 + e;
-      const bool ok = r < dim && col < vdim;
-      S[g * 4 + e] = (ok && has_prev) ? state[(size_t)r * vdim + col] : 0.f;
+#pragma unroll
+      for (int cc = 0; cc < CC; cc++) {
+        const int col = col0 + cc * CG + cl;
+        S[cc][g * 4 + e] = (r < dim && col < vdim && has_prev) ? state[(size_t)r * vdim + col] : 0.f;
+      }
       if (TMIX) U[g * 4 + e] = r < dim ? a.bonus[head * dim + r] : 0.f;
     }
 
@@ -220,8 +247,12 @@ __global__ void __launch_bounds__(LR_THREADS) linrec_scan_kernel(LinRecArgs a, T
     const int nt = min(TC, n_new - ch * TC);
     for (int tt = 0; tt < nt; tt++) {
       const float* row = stage[buf][tt];
-      const float v = row[3 * DP + cl];
-      float acc = 0.f;
+      float v[CC], acc[CC];
+#pragma unroll
+      for (int cc = 0; cc < CC; cc++) {
+        v[cc] = row[3 * DP + cc * CG + cl];
+        acc[cc] = 0.f;
+      }
 #pragma unroll
       for (int g = 0; g < RPL / 4; g++) {
         const int rb = (g * LPC + l) * 4;
@@ -231,20 +262,28 @@ __global__ void __launch_bounds__(LR_THREADS) linrec_scan_kernel(LinRecArgs a, T
         const float qq[4] = {q4.x, q4.y, q4.z, q4.w}, kk[4] = {k4.x, k4.y, k4.z, k4.w}, ww[4] = {w4.x, w4.y, w4.z, w4.w};
 #pragma unroll
         for (int e = 0; e < 4; e++) {
-          float& s = S[g * 4 + e];
-          if (TMIX) {
-            const float kv = kk[e] * v;
-            acc = fmaf(qq[e], fmaf(U[g * 4 + e], kv, s), acc);
-            s = fmaf(ww[e], s, kv);
-          } else {
-            s = fmaf(ww[e], s, kk[e] * v);
-            acc = fmaf(qq[e], s, acc);
+#pragma unroll
+          for (int cc = 0; cc < CC; cc++) {
+            float& s = S[cc][g * 4 + e];
+            if (TMIX) {
+              const float kv = kk[e] * v[cc];
+              acc[cc] = fmaf(qq[e], fmaf(U[g * 4 + e], kv, s), acc[cc]);
+              s = fmaf(ww[e], s, kv);
+            } else {
+              s = fmaf(ww[e], s, kk[e] * v[cc]);
+              acc[cc] = fmaf(qq[e], s, acc[cc]);
+            }
           }
         }
       }
 #pragma unroll
-      for (int o = LPC / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (l == 0 && col < vdim) a.o[(size_t)(r0 + ch * TC + tt) * hv + head * vdim + col] = acc;
+      for (int cc = 0; cc < CC; cc++) {
+        float t = acc[cc];
+#pragma unroll
+        for (int o = LPC / 2; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+        const int col = col0 + cc * CG + cl;
+        if (l == 0 && col < vdim) a.o[(size_t)(r0 + ch * TC + tt) * hv + head * vdim + col] = t * a.qmul;
+      }
     }
     __syncthreads();  // the buffer is free for the load of chunk ch + 2
   }
@@ -254,17 +293,27 @@ __global__ void __launch_bounds__(LR_THREADS) linrec_scan_kernel(LinRecArgs a, T
 #pragma unroll
     for (int e = 0; e < 4; e++) {
       const int r = (g * LPC + l) * 4 + e;
-      if (r < dim && col < vdim) state[(size_t)r * vdim + col] = S[g * 4 + e];
+#pragma unroll
+      for (int cc = 0; cc < CC; cc++) {
+        const int col = col0 + cc * CG + cl;
+        if (r < dim && col < vdim) state[(size_t)r * vdim + col] = S[cc][g * 4 + e];
+      }
     }
   TRACE_EXIT(tr);
 }
 
+template <int RPL, int LPC, int CC>
+static cudaError_t linrec_scan_launch_cc(cudaStream_t st, const LinRecArgs& a) {
+  const dim3 grid(a.n_seqs, a.H, ceil_div(a.vdim, LR_THREADS / LPC * CC));
+  if (a.tmix) (void)launch_k(linrec_scan_kernel<RPL, LPC, CC, true>, grid, dim3(LR_THREADS), 0, st, a, next_trace(41));
+  else (void)launch_k(linrec_scan_kernel<RPL, LPC, CC, false>, grid, dim3(LR_THREADS), 0, st, a, next_trace(41));
+  return cudaGetLastError();
+}
 template <int RPL, int LPC>
 static cudaError_t linrec_scan_launch(cudaStream_t st, const LinRecArgs& a) {
-  const dim3 grid(a.n_seqs, a.H, ceil_div(a.vdim, LR_THREADS / LPC));
-  if (a.tmix) (void)launch_k(linrec_scan_kernel<RPL, LPC, true>, grid, dim3(LR_THREADS), 0, st, a, next_trace(41));
-  else (void)launch_k(linrec_scan_kernel<RPL, LPC, false>, grid, dim3(LR_THREADS), 0, st, a, next_trace(41));
-  return cudaGetLastError();
+  // two columns per thread where a head has that many columns
+  if (a.vdim >= 2 * (LR_THREADS / LPC)) return linrec_scan_launch_cc<RPL, LPC, 2>(st, a);
+  return linrec_scan_launch_cc<RPL, LPC, 1>(st, a);
 }
 
 cudaError_t launch_linrec_scan(cudaStream_t st, const LinRecArgs& a) {
@@ -287,8 +336,45 @@ __global__ void __launch_bounds__(256) linrec_out_kernel(LinRecArgs a, Trace tr)
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const int vdim = a.vdim;
   OT* out = (OT*)a.out + (size_t)t * a.o_ld;
+  // 16-byte loads when every row and head starts on a 16-byte boundary
+  const bool vec = (vdim % 4) == 0 && vdim <= 512 && (a.gate.ld % 4) == 0 && (a.gate.stride % 4) == 0 &&
+                   (reinterpret_cast<size_t>(a.gate.p) % 16) == 0 && (a.onorm_ld % 4) == 0;
   for (int h = blockIdx.y * nw + warp; h < a.H; h += gridDim.y * nw) {
     const float* o = a.o + (size_t)t * a.H * vdim + (size_t)h * vdim;
+    if (vec) {
+      // four neighbouring columns per lane, all loads (read-outs, gate slices, weights) before the arithmetic
+      constexpr int MJ = 4;  // vdim <= 512
+      float4 ov[MJ], gv[MJ];
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < MJ; j++) {
+        const int i = lane * 4 + 128 * j;
+        if (i < vdim) {
+          ov[j] = *reinterpret_cast<const float4*>(o + i);
+          const float* gp = a.gate.p + (size_t)t * a.gate.ld + h * vdim + i;
+          gv[j] = *reinterpret_cast<const float4*>(gp);
+          for (int sl = 1; sl < a.gate.S; sl++) {
+            const float4 x = *reinterpret_cast<const float4*>(gp + (size_t)sl * a.gate.stride);
+            gv[j].x += x.x; gv[j].y += x.y; gv[j].z += x.z; gv[j].w += x.w;
+          }
+          ss += ov[j].x * ov[j].x + ov[j].y * ov[j].y + ov[j].z * ov[j].z + ov[j].w * ov[j].w;
+        }
+      }
+      const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)vdim + a.eps);
+      const float* w = a.onorm_w + (size_t)h * a.onorm_ld;
+#pragma unroll
+      for (int j = 0; j < MJ; j++) {
+        const int i = lane * 4 + 128 * j;
+        if (i < vdim) {
+          const float4 w4 = *reinterpret_cast<const float4*>(w + i);
+          const float r[4] = {ov[j].x * inv * w4.x * silu(gv[j].x), ov[j].y * inv * w4.y * silu(gv[j].y),
+                              ov[j].z * inv * w4.z * silu(gv[j].z), ov[j].w * inv * w4.w * silu(gv[j].w)};
+#pragma unroll
+          for (int e = 0; e < 4; e++) out[h * vdim + i + e] = from_f32<OT>(r[e]);
+        }
+      }
+      continue;
+    }
     float ss = 0.f;
     for (int i = lane; i < vdim; i += 32) ss += o[i] * o[i];
     const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)vdim + a.eps);
