@@ -163,17 +163,17 @@ __global__ void __launch_bounds__(1024) winattn_prep_conv_kernel(WinAttnArgs a, 
   pdl_wait();
   const int t = blockIdx.x;
   const int n_q = a.H * a.dim, n_k = a.G * a.dim, n_v = a.G * a.vdim, n_ch = n_q + n_k + n_v;
-  // sequence of the row: one row per sequence in a decode step, else a search through the offsets
-  int s = t;
-  if (a.T != a.n_seqs) {
-    int lo = 0, hi = a.n_seqs - 1;
-    while (lo < hi) {
-      const int mid = (lo + hi + 1) >> 1;
-      if (a.cu_q[mid] <= t) lo = mid;
-      else hi = mid - 1;
-    }
-    s = lo;
+  // sequence of the row: one row per sequence in a decode step; else every thread tests one
+  // sequence's range (one round trip instead of a chain of dependent loads)
+  __shared__ int s_seq;
+  if (a.T == a.n_seqs) {
+    if (threadIdx.x == 0) s_seq = t;
+  } else {
+    for (int i = threadIdx.x; i < a.n_seqs; i += blockDim.x)
+      if (a.cu_q[i] <= t && t < a.cu_q[i + 1]) s_seq = i;
   }
+  __syncthreads();
+  const int s = s_seq;
   const int r0 = a.cu_q[s];
   const int li = t - r0, pos = c.positions[t];
   const int keep = c.taps - 1;

@@ -1354,13 +1354,15 @@ extern "C" int nvllm_create_layered(const nvllm_layered_config* c, const nvllm_l
       LayerRun r;
       r.layer = l; r.pass_start = pass_start;
       const nvllm_layer_spec& s = h->ll[l].s;
-      r.state_off = h->state_slot_floats;
+      // every piece starts on a 16-byte boundary (the kernels read them with 16-byte loads)
+      auto up4 = [](size_t n) { return (n + 3) / 4 * 4; };
+      r.state_off = up4(h->state_slot_floats);
       if (s.mixer == NVLLM_MIXER_GLA) {
-        h->state_slot_floats += (size_t)s.heads * s.dim * s.vdim;
+        h->state_slot_floats = up4(r.state_off + (size_t)s.heads * s.dim * s.vdim);
       } else {
-        r.tail_off = r.state_off + (size_t)s.heads2 * s.dim2 * s.dim2;
-        r.shift_off = r.tail_off + (size_t)(s.conv - 1) * h->ll[l].conv_ch;
-        h->state_slot_floats = r.shift_off + (size_t)W;
+        r.tail_off = up4(r.state_off + (size_t)s.heads2 * s.dim2 * s.dim2);
+        r.shift_off = up4(r.tail_off + (size_t)(s.conv - 1) * h->ll[l].conv_ch);
+        h->state_slot_floats = up4(r.shift_off + (size_t)W);
       }
       h->runs.push_back(r);
     };

@@ -11,15 +11,14 @@
 //   linrec_prep_kernel   per tile of tokens: split-K sums of the projections, q scaled, the second step of
 //                        the decay's projection (fp32 FMA, the inner size is small) and the decay itself —
 //                        logarithms, exponentials and sigmoids in fp32 (log-sigmoid form, no overflow).
-//   linrec_scan_kernel   CTA = (sequence, head, CC * 128 / LPC value columns).  A column of the state is
-//                        independent of the others: it lives in the registers of LPC lanes (a lane holds
-//                        its rows of CC columns, so a row's q / k / decay is read once for CC updates)
-//                        (RPL rows each, rows dealt in groups of four so that the lanes' 16-byte
-//                        shared-memory reads of q / k / decay do not collide); per token one
-//                        pass over the rows and log2(LPC) shuffles.  Token inputs are staged
-//                        through shared memory in chunks, the next chunk's loads are in flight
-//                        (cp.async) while the current one is scanned.  State read from the slot when the sequence
-//                        has earlier tokens, written back at the end.
+//   linrec_scan_kernel   CTA = (sequence, head, 32 CC value columns), NW warps.  A column of the state is
+//                        independent of the others; a warp holds a slice of the rows (RPL each, dealt in
+//                        groups of four), a lane CC columns of that slice in registers.  Per token one pass
+//                        over the rows; the lanes of a warp read the same q / k / decay entries (broadcast
+//                        16-byte loads).  Token inputs are staged through shared memory in chunks, the next
+//                        chunk's loads in flight (cp.async) while the current one is scanned; the warps'
+//                        partial read-outs meet in shared memory once per chunk.  State read from the slot
+//                        when the sequence has earlier tokens, written back at the end.
 //   linrec_out_kernel    per token, a warp per head: RMS over vdim, weight, silu(gate) -> act dtype.
 //   token_shift_kernel   the inputs of time mixing's projections: h_t + (h_{t-1} - h_t) mu_s.
 //   roll_tails_kernel    after a step, the last inputs of a short convolution / token shift become
@@ -176,22 +175,24 @@ cudaError_t launch_linrec_prep(cudaStream_t st, const LinRecArgs& a) {
 }
 
 // ------------------------------------------------------------------ scan over tokens
-constexpr int LR_THREADS = 128;
-
-// CC: value columns per thread (the q / k / decay reads of a row are shared by them)
-template <int RPL, int LPC, int CC, bool TMIX>
-__global__ void __launch_bounds__(LR_THREADS) linrec_scan_kernel(LinRecArgs a, Trace tr) {
+// A warp holds one slice of the state's rows (RPL rows, dealt in groups of four), its lanes the
+// value columns (CC each): all lanes of a warp read the SAME q / k / decay entries — one
+// broadcast per 16-byte load instead of a pass per quarter warp — and the NW warps' partial
+// read-outs of a chunk of tokens meet in shared memory once per chunk.
+template <int RPL, int NW, int CC, bool TMIX>
+__global__ void __launch_bounds__(32 * NW) linrec_scan_kernel(LinRecArgs a, Trace tr) {
   TRACE_ENTRY(tr);
   pdl_launch_dependents();
-  constexpr int DP = RPL * LPC;           // rows of the state, padded
-  constexpr int CG = LR_THREADS / LPC;    // column groups = threads along the columns
-  constexpr int VC = CG * CC;             // value columns of this CTA
-  constexpr int TC = DP >= 256 ? 4 : (DP >= 128 ? 8 : 16);  // tokens per staged chunk
+  constexpr int NT = 32 * NW;
+  constexpr int DP = RPL * NW;            // rows of the state, padded
+  constexpr int VC = 32 * CC;             // value columns of this CTA
+  constexpr int TC = DP >= 256 ? 4 : 8;   // tokens per staged chunk
   constexpr int ROW = 3 * DP + VC;        // floats of one staged token: q | k | decay | v
   __shared__ __align__(16) float stage[2][TC][ROW];
+  __shared__ float part[NW][TC][VC];
   const int seq = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * VC;
   const int tid = threadIdx.x;
-  const int cl = tid / LPC, l = tid % LPC;  // column group, lane within the column
+  const int l = tid >> 5, lane = tid & 31;  // row slice, column group
   const int dim = a.dim, vdim = a.vdim, hd = a.H * dim, hv = a.H * vdim;
   pdl_wait();
   const int r0 = a.cu_q[seq], n_new = a.cu_q[seq + 1] - r0;
@@ -207,13 +208,13 @@ __global__ void __launch_bounds__(LR_THREADS) linrec_scan_kernel(LinRecArgs a, T
   const size_t v_ld = direct ? (size_t)a.v.ld : (size_t)hv;
   auto load_chunk = [&](int t0, int buf) {
     const int nt = min(TC, n_new - t0);
-    for (int i = tid; i < TC * 3 * DP; i += LR_THREADS) {
-      const int tt = i / (3 * DP), j = i % (3 * DP), part = j / DP, r = j % DP;
+    for (int i = tid; i < TC * 3 * DP; i += NT) {
+      const int tt = i / (3 * DP), j = i % (3 * DP), pt = j / DP, r = j % DP;
       const bool ok = tt < nt && r < dim;
-      const float* src = part_p[part] + (size_t)(r0 + t0 + (ok ? tt : 0)) * part_ld[part] + head * dim + (ok ? r : 0);
+      const float* src = part_p[pt] + (size_t)(r0 + t0 + (ok ? tt : 0)) * part_ld[pt] + head * dim + (ok ? r : 0);
       lr_cp_async4(smem_addr(&stage[buf][tt][j]), src, ok);
     }
-    for (int i = tid; i < TC * VC; i += LR_THREADS) {
+    for (int i = tid; i < TC * VC; i += NT) {
       const int tt = i / VC, c = i % VC;
       const bool ok = tt < nt && col0 + c < vdim;
       const float* src = v_p + (size_t)(r0 + t0 + (ok ? tt : 0)) * v_ld + head * vdim + (ok ? col0 + c : 0);
@@ -228,10 +229,10 @@ __global__ void __launch_bounds__(LR_THREADS) linrec_scan_kernel(LinRecArgs a, T
   for (int g = 0; g < RPL / 4; g++)
 #pragma unroll
     for (int e = 0; e < 4; e++) {
-      const int r = (g * LPC + l) * 4 + e;
+      const int r = (g * NW + l) * 4 + e;
 #pragma unroll
       for (int cc = 0; cc < CC; cc++) {
-        const int col = col0 + cc * CG + cl;
+        const int col = col0 + cc * 32 + lane;
         S[cc][g * 4 + e] = (r < dim && col < vdim && has_prev) ? state[(size_t)r * vdim + col] : 0.f;
       }
       if (TMIX) U[g * 4 + e] = r < dim ? a.bonus[head * dim + r] : 0.f;
@@ -245,17 +246,19 @@ __global__ void __launch_bounds__(LR_THREADS) linrec_scan_kernel(LinRecArgs a, T
     cp_async_wait<1>();
     __syncthreads();
     const int nt = min(TC, n_new - ch * TC);
-    for (int tt = 0; tt < nt; tt++) {
+#pragma unroll
+    for (int tt = 0; tt < TC; tt++) {
+      if (tt >= nt) break;
       const float* row = stage[buf][tt];
       float v[CC], acc[CC];
 #pragma unroll
       for (int cc = 0; cc < CC; cc++) {
-        v[cc] = row[3 * DP + cc * CG + cl];
+        v[cc] = row[3 * DP + cc * 32 + lane];
         acc[cc] = 0.f;
       }
 #pragma unroll
       for (int g = 0; g < RPL / 4; g++) {
-        const int rb = (g * LPC + l) * 4;
+        const int rb = (g * NW + l) * 4;
         const float4 q4 = *reinterpret_cast<const float4*>(row + rb);
         const float4 k4 = *reinterpret_cast<const float4*>(row + DP + rb);
         const float4 w4 = *reinterpret_cast<const float4*>(row + 2 * DP + rb);
@@ -277,43 +280,45 @@ __global__ void __launch_bounds__(LR_THREADS) linrec_scan_kernel(LinRecArgs a, T
         }
       }
 #pragma unroll
-      for (int cc = 0; cc < CC; cc++) {
-        float t = acc[cc];
-#pragma unroll
-        for (int o = LPC / 2; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
-        const int col = col0 + cc * CG + cl;
-        if (l == 0 && col < vdim) a.o[(size_t)(r0 + ch * TC + tt) * hv + head * vdim + col] = t * a.qmul;
-      }
+      for (int cc = 0; cc < CC; cc++) part[l][tt][cc * 32 + lane] = acc[cc];
     }
-    __syncthreads();  // the buffer is free for the load of chunk ch + 2
+    __syncthreads();  // the slices' partial read-outs are in; the staged chunk has been consumed
+    for (int i = tid; i < nt * VC; i += NT) {
+      const int tt = i / VC, c = i % VC;
+      float t = 0.f;
+#pragma unroll
+      for (int w = 0; w < NW; w++) t += part[w][tt][c];
+      if (col0 + c < vdim) a.o[(size_t)(r0 + ch * TC + tt) * hv + head * vdim + col0 + c] = t * a.qmul;
+    }
   }
   cp_async_wait<0>();
 #pragma unroll
   for (int g = 0; g < RPL / 4; g++)
 #pragma unroll
     for (int e = 0; e < 4; e++) {
-      const int r = (g * LPC + l) * 4 + e;
+      const int r = (g * NW + l) * 4 + e;
 #pragma unroll
       for (int cc = 0; cc < CC; cc++) {
-        const int col = col0 + cc * CG + cl;
+        const int col = col0 + cc * 32 + lane;
         if (r < dim && col < vdim) state[(size_t)r * vdim + col] = S[cc][g * 4 + e];
       }
     }
   TRACE_EXIT(tr);
 }
 
-template <int RPL, int LPC, int CC>
+template <int RPL, int NW, int CC>
 static cudaError_t linrec_scan_launch_cc(cudaStream_t st, const LinRecArgs& a) {
-  const dim3 grid(a.n_seqs, a.H, ceil_div(a.vdim, LR_THREADS / LPC * CC));
-  if (a.tmix) (void)launch_k(linrec_scan_kernel<RPL, LPC, CC, true>, grid, dim3(LR_THREADS), 0, st, a, next_trace(41));
-  else (void)launch_k(linrec_scan_kernel<RPL, LPC, CC, false>, grid, dim3(LR_THREADS), 0, st, a, next_trace(41));
+  const dim3 grid(a.n_seqs, a.H, ceil_div(a.vdim, 32 * CC));
+  if (a.tmix) (void)launch_k(linrec_scan_kernel<RPL, NW, CC, true>, grid, dim3(32 * NW), 0, st, a, next_trace(41));
+  else (void)launch_k(linrec_scan_kernel<RPL, NW, CC, false>, grid, dim3(32 * NW), 0, st, a, next_trace(41));
   return cudaGetLastError();
 }
-template <int RPL, int LPC>
+template <int RPL, int NW>
 static cudaError_t linrec_scan_launch(cudaStream_t st, const LinRecArgs& a) {
-  // two columns per thread where a head has that many columns
-  if (a.vdim >= 2 * (LR_THREADS / LPC)) return linrec_scan_launch_cc<RPL, LPC, 2>(st, a);
-  return linrec_scan_launch_cc<RPL, LPC, 1>(st, a);
+  // more columns per lane where a head has that many: a row's q / k / decay is read once for all of them
+  if (RPL <= 16 && a.vdim >= 128) return linrec_scan_launch_cc<RPL, NW, 4>(st, a);
+  if (a.vdim >= 64) return linrec_scan_launch_cc<RPL, NW, 2>(st, a);
+  return linrec_scan_launch_cc<RPL, NW, 1>(st, a);
 }
 
 cudaError_t launch_linrec_scan(cudaStream_t st, const LinRecArgs& a) {
@@ -409,16 +414,35 @@ __global__ void __launch_bounds__(256) token_shift_kernel(int T, int n_seqs, int
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
-  const int s = T == n_seqs ? t : lr_seq_of_row(cu_q, n_seqs, t);
+  // the row's sequence: every thread tests one sequence's range (one round trip, no dependent chain)
+  __shared__ int s_seq;
+  if (T == n_seqs) {
+    if (threadIdx.x == 0) s_seq = t;
+  } else {
+    for (int i = threadIdx.x; i < n_seqs; i += blockDim.x)
+      if (cu_q[i] <= t && t < cu_q[i + 1]) s_seq = i;
+  }
+  __syncthreads();
+  const int s = s_seq;
   const int r0 = cu_q[s];
   const bool in_step = t > r0;
   const bool in_slot = !in_step && positions[t] > 0;
   const float* tail = state_pool + (size_t)state_slots[s] * slot_floats + tail_off;
-  for (int i = threadIdx.x; i < W; i += blockDim.x) {
-    const float x = to_f32(h[(size_t)t * W + i]);
-    const float xp = in_step ? to_f32(h[(size_t)(t - 1) * W + i]) : (in_slot ? tail[i] : 0.f);
-    const float d = xp - x;
-    for (int m = 0; m < n_mix; m++) out[((size_t)m * T + t) * W + i] = from_f32<AT>(fmaf(d, mu[(size_t)m * W + i], x));
+  for (int i = threadIdx.x * 8; i < W; i += blockDim.x * 8) {  // W is a multiple of 8
+    float x[8], xp[8];
+    load8(h + (size_t)t * W + i, x);
+    if (in_step) load8(h + (size_t)(t - 1) * W + i, xp);
+    else if (in_slot) load8(tail + i, xp);
+    else
+#pragma unroll
+      for (int e = 0; e < 8; e++) xp[e] = 0.f;
+    for (int m = 0; m < n_mix; m++) {
+      float w[8], y[8];
+      load8(mu + (size_t)m * W + i, w);
+#pragma unroll
+      for (int e = 0; e < 8; e++) y[e] = fmaf(xp[e] - x[e], w[e], x[e]);
+      store8(out + ((size_t)m * T + t) * W + i, y);
+    }
   }
   TRACE_EXIT(tr);
 }
@@ -428,10 +452,10 @@ cudaError_t launch_token_shift(cudaStream_t st, int adt, int T, int n_seqs, int 
                                const float* state_pool, size_t slot_floats, size_t tail_off, void* out) {
   if (T <= 0) return cudaSuccess;
   if (adt == DT_F32)
-    (void)launch_k(token_shift_kernel<float>, dim3(T), dim3(256), 0, st, T, n_seqs, W, n_mix, (const float*)h, mu, cu_q,
+    (void)launch_k(token_shift_kernel<float>, dim3(T), dim3(128), 0, st, T, n_seqs, W, n_mix, (const float*)h, mu, cu_q,
                    positions, state_slots, state_pool, slot_floats, tail_off, (float*)out, next_trace(43));
   else
-    (void)launch_k(token_shift_kernel<bf16>, dim3(T), dim3(256), 0, st, T, n_seqs, W, n_mix, (const bf16*)h, mu, cu_q,
+    (void)launch_k(token_shift_kernel<bf16>, dim3(T), dim3(128), 0, st, T, n_seqs, W, n_mix, (const bf16*)h, mu, cu_q,
                    positions, state_slots, state_pool, slot_floats, tail_off, (bf16*)out, next_trace(43));
   return cudaGetLastError();
 }
