@@ -154,13 +154,16 @@ cudaError_t launch_winattn_prep(cudaStream_t st, int qdt, int kvdt, const WinAtt
 // rows (this step's rows through the partials, earlier ones through the slot's tail), q and k
 // staged in shared memory with their sums of squares, v straight into the pool, the gates'
 // sigmoids out.  Pass 2: the two whole-row norms, weights, rotation, Q and K out.
-template <typename QT, typename KT>
+// TAPS > 0: the number of taps at compile time (no predicates around the taps' loads); 0: c.taps <= 8.
+template <typename QT, typename KT, int TAPS>
 __global__ void __launch_bounds__(1024) winattn_prep_conv_kernel(WinAttnArgs a, ConvAttnPrep c, Trace tr) {
   TRACE_ENTRY(tr);
   pdl_launch_dependents();
   extern __shared__ float qk[];  // [n_q + n_k] convolved
   __shared__ float red[32];
   pdl_wait();
+  constexpr int MT = TAPS > 0 ? TAPS : 8;
+  const int taps = TAPS > 0 ? TAPS : c.taps;
   const int t = blockIdx.x;
   const int n_q = a.H * a.dim, n_k = a.G * a.dim, n_v = a.G * a.vdim, n_ch = n_q + n_k + n_v;
   // sequence of the row: one row per sequence in a decode step; else every thread tests one
@@ -176,52 +179,65 @@ __global__ void __launch_bounds__(1024) winattn_prep_conv_kernel(WinAttnArgs a, 
   const int s = s_seq;
   const int r0 = a.cu_q[s];
   const int li = t - r0, pos = c.positions[t];
-  const int keep = c.taps - 1;
+  const int keep = taps - 1;
   const float* tail = c.state_pool + (size_t)c.state_slots[s] * c.slot_floats + c.tail_off;
   const int slot = a.slots[t];
   const int blk = slot / KV_BLOCK, off = slot % KV_BLOCK;
   // where tap j's input lives is the same for every channel of the row: a row of this step's
   // partials, a row of the slot's tail, or nowhere (before the sequence's start)
-  const float* src[8];
-  bool from_step[8];
+  const float* src[MT];
+  float bmul[MT];  // 1: the row still wants the projection's bias
 #pragma unroll
-  for (int j = 0; j < 8; j++) {
+  for (int j = 0; j < MT; j++) {
     src[j] = nullptr;
-    from_step[j] = false;
-    if (j < c.taps) {
+    bmul[j] = 0.f;
+    if (j < taps) {
       const int back = keep - j;  // input `back` positions before this token
-      if (back <= li) { src[j] = a.in_p + (size_t)(t - back) * a.in_ld; from_step[j] = true; }
+      if (back <= li) { src[j] = a.in_p + (size_t)(t - back) * a.in_ld; bmul[j] = 1.f; }
       else if (back <= pos) src[j] = tail + (size_t)(keep - (back - li)) * n_ch;
     }
   }
-  float ssq = 0.f, ssk = 0.f;
-  for (int ch = threadIdx.x; ch < n_ch; ch += blockDim.x) {
+  const bool one = a.in_S == 1;
+  auto conv_at = [&](int ch) {
     const float b = c.bias ? c.bias[ch] : 0.f;
-    float u[8];
+    float u[MT], wv[MT];
 #pragma unroll
-    for (int j = 0; j < 8; j++) {  // all the taps' loads first
+    for (int j = 0; j < MT; j++) {  // all the loads first
       u[j] = 0.f;
-      if (j < c.taps && src[j]) {
-        if (a.in_S == 1) u[j] = src[j][ch] + (from_step[j] ? b : 0.f);  // one slice: nothing to sum, no loop around the load
-        else u[j] = from_step[j] ? sum_slices(src[j] + ch, a.in_S, a.in_stride) + b : src[j][ch];
+      wv[j] = j < taps ? c.conv_w[ch * taps + j] : 0.f;
+      if (j < taps && src[j]) {
+        if (one || bmul[j] == 0.f) u[j] = src[j][ch];  // one slice (or a tail row): nothing to sum
+        else u[j] = sum_slices(src[j] + ch, a.in_S, a.in_stride);
       }
     }
     float y = 0.f;
 #pragma unroll
-    for (int j = 0; j < 8; j++)
-      if (j < c.taps) y = fmaf(c.conv_w[(size_t)ch * c.taps + j], u[j], y);
-    if (ch < n_q) { qk[ch] = y; ssq += y * y; }
-    else if (ch < n_q + n_k) { qk[ch] = y; ssk += y * y; }
-    else {
-      const int vc = ch - n_q - n_k, g = vc / a.vdim, i = vc % a.vdim;
-      ((KT*)a.vpool)[(((size_t)blk * a.G + g) * KV_BLOCK + off) * a.vdim + i] = from_f32<KT>(y);
-    }
+    for (int j = 0; j < MT; j++) y = fmaf(wv[j], fmaf(bmul[j], b, u[j]), y);
+    return y;
+  };
+  float ssq = 0.f, ssk = 0.f;
+  for (int ch = threadIdx.x; ch < n_q; ch += blockDim.x) {
+    const float y = conv_at(ch);
+    qk[ch] = y;
+    ssq += y * y;
+  }
+  for (int ch = n_q + threadIdx.x; ch < n_q + n_k; ch += blockDim.x) {
+    const float y = conv_at(ch);
+    qk[ch] = y;
+    ssk += y * y;
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (int g = warp; g < a.G; g += nw) {  // values: a warp per head, no division per element
+    KT* vd = (KT*)a.vpool + (((size_t)blk * a.G + g) * KV_BLOCK + off) * a.vdim;
+    for (int i = lane; i < a.vdim; i += 32) vd[i] = from_f32<KT>(conv_at(n_q + n_k + g * a.vdim + i));
   }
   if (c.gate_out) {
     const int n_g = a.H * a.vdim;
+    const float* gp = a.in_p + (size_t)t * a.in_ld + n_ch;
+    float* go = c.gate_out + (size_t)t * c.gate_ld;
     for (int i = threadIdx.x; i < n_g; i += blockDim.x) {
-      const float z = sum_slices(a.in_p + (size_t)t * a.in_ld + n_ch + i, a.in_S, a.in_stride);
-      c.gate_out[(size_t)t * c.gate_ld + i] = 1.0f / (1.0f + expf(-z));
+      const float z = one ? gp[i] : sum_slices(gp + i, a.in_S, a.in_stride);
+      go[i] = 1.0f / (1.0f + expf(-z));
     }
   }
   const float inv_q = 1.0f / sqrtf(block_sum(ssq, red) / (float)n_q + a.eps);
@@ -229,24 +245,43 @@ __global__ void __launch_bounds__(1024) winattn_prep_conv_kernel(WinAttnArgs a, 
   const float* cs = c.cosT + (size_t)t * c.rot_half;
   const float* sn = c.sinT + (size_t)t * c.rot_half;
   const int rot = 2 * c.rot_half;
-  for (int ch = threadIdx.x; ch < n_q + n_k; ch += blockDim.x) {
-    const bool isq = ch < n_q;
-    const int cc = isq ? ch : ch - n_q;
-    const int hh = cc / a.dim, i = cc % a.dim;
+  for (int hh = warp; hh < a.H + a.G; hh += nw) {  // a warp per query / key head
+    const bool isq = hh < a.H;
+    const int base = hh * a.dim;                    // first channel of the head in qk[]
     const float inv = isq ? inv_q : inv_k;
-    const float* w = isq ? c.qnorm_w : c.knorm_w;
-    float v = qk[ch] * inv * w[cc];
-    if (i < rot) {
-      const int ip = i < c.rot_half ? i + c.rot_half : i - c.rot_half;  // the entry it is paired with
-      const int pch = ch - i + ip;
-      const float o = qk[pch] * inv * w[cc - i + ip];
-      const int f = i < c.rot_half ? i : ip;
-      v = i < c.rot_half ? v * cs[f] - o * sn[f] : v * cs[f] + o * sn[f];
+    const float* w = isq ? c.qnorm_w + base : c.knorm_w + (base - n_q);
+    const float* x = qk + base;
+    QT* qd = isq ? (QT*)a.q + (size_t)t * n_q + base : nullptr;
+    KT* kd = isq ? nullptr : (KT*)a.kpool + (((size_t)blk * a.G + (hh - a.H)) * KV_BLOCK + off) * a.dim;
+    for (int i = lane; i < a.dim; i += 32) {
+      float v = x[i] * inv * w[i];
+      if (i < rot) {
+        const int ip = i < c.rot_half ? i + c.rot_half : i - c.rot_half;  // the entry it is paired with
+        const float o = x[ip] * inv * w[ip];
+        const int f = i < c.rot_half ? i : ip;
+        v = i < c.rot_half ? v * cs[f] - o * sn[f] : v * cs[f] + o * sn[f];
+      }
+      if (isq) qd[i] = from_f32<QT>(v);
+      else kd[i] = from_f32<KT>(v);
     }
-    if (isq) ((QT*)a.q)[(size_t)t * n_q + cc] = from_f32<QT>(v);
-    else ((KT*)a.kpool)[(((size_t)blk * a.G + hh) * KV_BLOCK + off) * a.dim + i] = from_f32<KT>(v);
   }
   TRACE_EXIT(tr);
+}
+
+template <typename QT, typename KT>
+static void winattn_prep_conv_launch(cudaStream_t st, const WinAttnArgs& a, const ConvAttnPrep& c, dim3 block, size_t smem) {
+#define WPC(T_)                                                                                                        \
+  {                                                                                                                    \
+    if (smem > 48 * 1024)                                                                                              \
+      cudaFuncSetAttribute(winattn_prep_conv_kernel<QT, KT, T_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    (void)launch_k(winattn_prep_conv_kernel<QT, KT, T_>, dim3(a.T), block, smem, st, a, c, next_trace(38));            \
+  }
+  if (c.taps == 1) WPC(1)
+  else if (c.taps == 2) WPC(2)
+  else if (c.taps == 3) WPC(3)
+  else if (c.taps == 4) WPC(4)
+  else WPC(0)
+#undef WPC
 }
 
 cudaError_t launch_winattn_prep_conv(cudaStream_t st, int qdt, int kvdt, const WinAttnArgs& a, const ConvAttnPrep& c) {
@@ -255,15 +290,9 @@ cudaError_t launch_winattn_prep_conv(cudaStream_t st, int qdt, int kvdt, const W
   const size_t smem = (size_t)(a.H + a.G) * a.dim * sizeof(float);
   // few rows (decode): the row's channels spread over more threads
   const dim3 block(a.T >= 1024 ? 256 : 1024);
-  if (qdt == DT_F32 && kvdt == DT_F32) {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(winattn_prep_conv_kernel<float, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    (void)launch_k(winattn_prep_conv_kernel<float, float>, dim3(a.T), block, smem, st, a, c, next_trace(38));
-  } else if (qdt == DT_BF16 && kvdt == DT_BF16) {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(winattn_prep_conv_kernel<bf16, bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    (void)launch_k(winattn_prep_conv_kernel<bf16, bf16>, dim3(a.T), block, smem, st, a, c, next_trace(38));
-  } else {
-    return cudaErrorInvalidValue;
-  }
+  if (qdt == DT_F32 && kvdt == DT_F32) winattn_prep_conv_launch<float, float>(st, a, c, block, smem);
+  else if (qdt == DT_BF16 && kvdt == DT_BF16) winattn_prep_conv_launch<bf16, bf16>(st, a, c, block, smem);
+  else return cudaErrorInvalidValue;
   return cudaGetLastError();
 }
 
