@@ -315,9 +315,13 @@ static cudaError_t linrec_scan_launch_cc(cudaStream_t st, const LinRecArgs& a) {
 }
 template <int RPL, int NW>
 static cudaError_t linrec_scan_launch(cudaStream_t st, const LinRecArgs& a) {
-  // more columns per lane where a head has that many: a row's q / k / decay is read once for all of them
-  if (RPL <= 16 && a.vdim >= 128) return linrec_scan_launch_cc<RPL, NW, 4>(st, a);
-  if (a.vdim >= 64) return linrec_scan_launch_cc<RPL, NW, 2>(st, a);
+  // more columns per lane where a head has that many (a row's q / k / decay is read once for all of
+  // them) — as long as the grid still fills the GPU twice over: a sequence's tokens are scanned in
+  // order, so few long sequences want many narrow CTAs
+  const long units = (long)a.n_seqs * a.H;
+  const long want = 2 * 148;
+  if (RPL <= 16 && a.vdim >= 128 && units * ceil_div(a.vdim, 128) >= want) return linrec_scan_launch_cc<RPL, NW, 4>(st, a);
+  if (a.vdim >= 64 && units * ceil_div(a.vdim, 64) >= want) return linrec_scan_launch_cc<RPL, NW, 2>(st, a);
   return linrec_scan_launch_cc<RPL, NW, 1>(st, a);
 }
 
