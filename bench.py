@@ -563,7 +563,7 @@ def lazovik_cfg(width, n_layers, vocab, every, g_heads, g_dim, g_vdim, a_heads, 
         else:
             kw = dict(mixer=C.MIXER_GLA, heads=g_heads, dim=g_dim, vdim=g_vdim, tau=16.0, lowrank=rank)
         layers.append(C.LayerSpec(**kw, **moe))
-    lp = loop or (0, 0, 1)
+    lp = loop or (0, 0, 0)
     return C.ListedModelConfig("lazovik", vocab, width, tuple(layers), 1e-5, arch=C.ARCH_LAZOVIK,
                                block_style=C.LBLOCK_SEQUENTIAL_PRENORM, loop_start=lp[0], loop_stop=lp[1], loop_times=lp[2])
 

@@ -272,8 +272,9 @@ typedef struct nvllm_layered_config {
   int32_t tied_head;       /* 1: logits = embed x (the table itself, without embedding_scale); no "head" tensor */
   float norm_offset;       /* norm weights are stored as w - norm_offset (1: "around zero") */
   int32_t num_state_slots; /* recurrent mixers: sequences that can hold state at once (<= 0: max_num_seqs) */
-  /* layers [loop_start, loop_stop) run loop_times times in a row with the same weights (loop_times <= 1: once);
-   * tensor "loop.step" [loop_times, hidden]: row t is added to x before pass t */
+  /* layers [loop_start, loop_stop) run loop_times times in a row with the same weights; tensor "loop.step"
+   * [loop_times, hidden]: row t is added to x before pass t (also when loop_times is 1).  loop_times < 1 or an
+   * empty range: no such run */
   int32_t loop_start, loop_stop, loop_times;
 } nvllm_layered_config;
 

@@ -479,13 +479,17 @@ class ListedModelConfig:
     norm_offset: float = 0.0
     loop_start: int = 0
     loop_stop: int = 0
-    loop_times: int = 1
+    loop_times: int = 0   # >= 1 with loop_stop > loop_start: layers [start, stop) run that often in a row
+
+    @property
+    def has_loop(self) -> bool:
+        return self.loop_times >= 1 and self.loop_stop > self.loop_start
 
     @property
     def runs(self) -> Tuple[int, ...]:
         """Layer indices in execution order (a repeated run of layers counts every pass)."""
         n = len(self.layers)
-        if self.loop_times <= 1:
+        if not self.has_loop:
             return tuple(range(n))
         return tuple(range(self.loop_start)) + tuple(range(self.loop_start, self.loop_stop)) * self.loop_times + \
             tuple(range(self.loop_stop, n))
@@ -503,7 +507,7 @@ class ListedModelConfig:
         d = {"embed": (self.vocab_size, self.hidden), "final.norm": (self.hidden,)}
         if not self.tied_head:
             d["head"] = (self.vocab_size, self.hidden)
-        if self.loop_times > 1:
+        if self.has_loop:
             d["loop.step"] = (self.loop_times, self.hidden)
         for i, l in enumerate(self.layers):
             d.update(l.tensor_shapes(i, self.hidden))
@@ -664,13 +668,13 @@ def lazovik_from_json(j: dict, shapes: Optional[dict] = None) -> ListedModelConf
     mixture of squared-ReLU experts with an always-on expert; a run of layers may repeat.
     `shapes`: tensor name -> shape of the checkpoint (sizes that only a tensor's shape gives)."""
     lp = j.get("loop") or {}
-    times = int(lp.get("times") or 1)
+    times = int(lp.get("times") or 0)  # a run that "repeats" once still opens its pass with the pass's vector
     return ListedModelConfig(
         name="lazovik", vocab_size=int(j["vocab"]), hidden=int(j["width"]),
         layers=tuple(_lazovik_layer(i, lc, shapes or {}) for i, lc in enumerate(j["layers"])),
         norm_eps=float(j["norm"]["eps"]), arch=ARCH_LAZOVIK, block_style=LBLOCK_SEQUENTIAL_PRENORM,
-        loop_start=int(lp.get("start") or 0) if times > 1 else 0,
-        loop_stop=int(lp.get("stop") or 0) if times > 1 else 0, loop_times=times)
+        loop_start=int(lp.get("start") or 0) if times >= 1 else 0,
+        loop_stop=int(lp.get("stop") or 0) if times >= 1 else 0, loop_times=times)
 
 
 def safetensors_shapes(model_dir: str) -> dict:

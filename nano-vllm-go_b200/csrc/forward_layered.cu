@@ -1011,7 +1011,8 @@ extern "C" int nvllm_create_layered(const nvllm_layered_config* c, const nvllm_l
   if (c->hidden % 8) return bad(-1, "width must be a multiple of 8");
   if (c->precision != NVLLM_PREC_FP32 && c->precision != NVLLM_PREC_BF16) return bad(-1, "precision");
   const bool pre_style = c->block_style == NVLLM_LBLOCK_SEQUENTIAL_PRENORM;
-  if (c->loop_times > 1 && (!pre_style || c->loop_start < 0 || c->loop_stop > c->num_layers || c->loop_start >= c->loop_stop))
+  const bool has_loop = c->loop_times >= 1 && c->loop_stop > c->loop_start;
+  if (has_loop && (!pre_style || c->loop_start < 0 || c->loop_stop > c->num_layers))
     return bad(-1, "a repeated run of layers needs the sequential pre-norm block style and 0 <= start < stop <= layers");
   for (int l = 0; l < c->num_layers; l++) {
     const nvllm_layer_spec& s = layers[l];
@@ -1134,7 +1135,7 @@ extern "C" int nvllm_create_layered(const nvllm_layered_config* c, const nvllm_l
     g.num_kv_heads = layers[0].kv_heads > 0 ? layers[0].kv_heads : layers[0].heads; g.head_dim = layers[0].dim;
     g.attention_type = NVLLM_ATTN_GQA; g.norm_type = NVLLM_NORM_RMS; g.position_type = NVLLM_POS_ROPE;
     g.activation_type = NVLLM_ACT_GELU; g.block_style = NVLLM_BLOCK_SEQUENTIAL;
-    if (c->loop_times > 1) {
+    if (has_loop) {
       h->loop_start = c->loop_start; h->loop_stop = c->loop_stop; h->loop_times = c->loop_times;
     }
   }
@@ -1366,7 +1367,7 @@ extern "C" int nvllm_create_layered(const nvllm_layered_config* c, const nvllm_l
       }
       h->runs.push_back(r);
     };
-    const bool loop = h->loop_times > 1;
+    const bool loop = h->loop_times >= 1 && h->loop_stop > h->loop_start;
     const int a0 = loop ? h->loop_start : 0, a1 = loop ? h->loop_stop : 0;
     for (int l = 0; l < a0; l++) add_run(l, -1);
     for (int t = 0; t < (loop ? h->loop_times : 0); t++)

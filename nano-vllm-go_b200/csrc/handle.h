@@ -233,7 +233,7 @@ struct nvllm_handle {
   // indexed by execution there), the vectors that open the passes of the repeated run [times][W]
   std::vector<nvllm::LayerRun> runs;
   float* loop_step = nullptr;
-  int loop_start = 0, loop_stop = 0, loop_times = 1;
+  int loop_start = 0, loop_stop = 0, loop_times = 0;  // times >= 1 with stop > start: a repeated run exists
   int block_style = 0, position_kind = 0;
   float norm_offset = 0.f;               // added to every norm weight at load
   double* pos_freq = nullptr;            // sinusoidal positions: 10000^(-2i / W), i < W / 2, on the device

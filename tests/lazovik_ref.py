@@ -178,7 +178,7 @@ def execution_order(cfg_json):
     """(layer, pass it opens or None): a repeated run of layers counts once per pass."""
     n = len(cfg_json["layers"])
     lp = cfg_json.get("loop")
-    if not lp or lp["times"] <= 1:
+    if not lp or lp["times"] < 1 or lp["stop"] <= lp["start"]:
         return [(i, None) for i in range(n)]
     order = [(i, None) for i in range(lp["start"])]
     for t in range(lp["times"]):

@@ -200,6 +200,8 @@ def test_config_reader_takes_every_size_from_the_file_and_the_tensor_shapes():
     assert specs[3].heads2 == 3 and specs[3].route_sigmoid == 1 and abs(specs[3].mix2_scale - 1.3) < 1e-6
     # no repeated run: the layers run once, in order
     assert C.lazovik_from_json(odd_model(), shapes_of(odd_model())).runs == (0, 1, 2)
+    once = C.lazovik_from_json(model([layer(gla()), layer(gla())], loop=(1, 2, 1)), {"l0.mix.a1": (8, 64), "l1.mix.a1": (8, 64)})
+    assert once.runs == (0, 1) and once.has_loop and once.tensor_shapes()["loop.step"] == (1, 64)
     with pytest.raises(ValueError):
         C.lazovik_from_json(model([dict(type="conv", mixer=gla()["mixer"], mlp=None)]), {})
     with pytest.raises(ValueError):  # the inner size of the decay projection is known from the checkpoint only
@@ -232,14 +234,16 @@ CASES = {
     "experts": lambda: [layer(gla(), moe(ff=32, experts=6, top=2, shared=0))],
     "experts_and_always_on": lambda: [layer(gla(), moe(ff=12, experts=4, top=4, shared=200))],
     "repeat": lambda: [layer(gla()), layer(par())],
+    "repeat_once": lambda: [layer(par()), layer(gla())],  # one pass: still opened by the pass's vector
 }
+LOOPS = {"repeat": (0, 2, 3), "repeat_once": (1, 2, 1)}
 
 
 @gpu
 @pytest.mark.parametrize("prec", PRECS)
 @pytest.mark.parametrize("case", sorted(CASES))
 def test_each_mechanism_alone(case, prec):
-    j = model(CASES[case](), loop=(0, 2, 3) if case == "repeat" else None)
+    j = model(CASES[case](), loop=LOOPS.get(case))
     cfg, w, eng = setup(j, prec)
     try:
         toks = prompt(j, 90, 1)
