@@ -500,6 +500,76 @@ def test_long_decoding_stays_on_the_reference():
         eng.close()
 
 
+# ------------------------------------------------------------------ GPU: models drawn at random
+def draw_model(rng):
+    """Sizes, head counts, layer order, chunks, constants and the repeated run all drawn."""
+    layers = []
+    for _ in range(int(rng.integers(2, 6))):
+        if rng.random() < 0.5:
+            mix = gla(heads=int(rng.integers(1, 7)), dim=int(rng.choice([8, 12, 16, 32, 48, 64, 96, 128])),
+                      vdim=int(rng.choice([8, 16, 24, 32, 64, 96, 128])), tau=float(rng.uniform(1, 32)), rank=int(rng.integers(2, 33)))
+        else:
+            kv, g = int(rng.integers(1, 5)), int(rng.choice([1, 2, 3, 4, 6]))
+            dim = int(rng.choice([8, 16, 32, 64, 128]))
+            sc = None if rng.random() < 0.4 else {"factor": float(rng.uniform(1.5, 8)), "original": int(rng.integers(16, 4096)),
+                                                  "fast": float(rng.uniform(4, 64)), "slow": float(rng.uniform(0.5, 2))}
+            mix = par(heads=kv * g, kv_heads=kv, dim=dim, vdim=int(rng.choice([8, 16, 32, 64, 128])), conv=int(rng.integers(1, 6)),
+                      chunk=int(rng.integers(1, 300)), rot_dims=int(rng.integers(1, dim // 2 + 1)) * 2,
+                      base=float(rng.choice([100.0, 10000.0, 500000.0])), scaling=sc, scale=float(dim ** -0.5 * rng.uniform(0.5, 2)),
+                      softcap=float(rng.choice([0.0, 5.0, 20.0, 50.0])), heads2=int(rng.integers(1, 5)),
+                      dim2=int(rng.choice([8, 16, 32, 64, 128])), rank=int(rng.integers(2, 33)),
+                      ls=float(rng.uniform(0.3, 1.5)), rs=float(rng.uniform(0.3, 1.5)))
+        mlp = None
+        if rng.random() < 0.8:
+            e = int(rng.integers(2, 21))
+            mlp = moe(ff=int(rng.integers(8, 100)), experts=e, top=int(rng.integers(1, min(4, e) + 1)),
+                      shared=0 if rng.random() < 0.3 else int(rng.integers(8, 120)))
+        layers.append(layer(mix, mlp))
+    loop = None
+    if rng.random() < 0.7:
+        a = int(rng.integers(0, len(layers)))
+        loop = (a, int(rng.integers(a + 1, len(layers) + 1)), int(rng.integers(1, 4)))
+    return model(layers, vocab=int(rng.integers(50, 500)), width=int(rng.choice([64, 96, 128, 192, 256])),
+                 eps=float(rng.choice([1e-5, 1e-6, 1e-4])), loop=loop)
+
+
+@gpu
+@pytest.mark.parametrize("seed", range(8))
+def test_models_drawn_at_random(seed):
+    """Whole prompt, then the same tokens in drawn portions with the last ones decoded, beside a
+    second request that comes and goes; fp32, every row."""
+    rng = np.random.default_rng(4000 + seed)
+    j = draw_model(rng)
+    cfg, w, eng = setup(j, C.PREC_FP32, seed=50 + seed)
+    try:
+        n = int(rng.integers(30, 330))
+        toks, other = prompt(j, n, 60 + seed), prompt(j, int(rng.integers(3, 120)), 70 + seed)
+        want, want_o = ref.forward(j, w, toks), ref.forward(j, w, other)
+        got, _ = eng.step([("w", toks, list(range(n)))])
+        check(got, want, C.PREC_FP32, "whole prompt")
+        eng.end("w")
+        rows, pos, po, ndec = [], 0, 0, int(rng.integers(1, 9))
+        while pos < n - ndec:
+            c = int(min(n - ndec - pos, rng.choice([2, 2, 3, 5, 17, 64, 100, 130])))
+            entries = [("p", toks[pos:pos + c], list(range(c)))]
+            if po < len(other):
+                co = int(min(len(other) - po, rng.choice([1, 2, 9, 40])))
+                entries.append(("o", other[po:po + co], [co - 1]))
+            out, _ = eng.step(entries)
+            rows.append(out[:c])
+            if len(entries) > 1:
+                check(out[c:], want_o[po + co - 1:po + co], C.PREC_FP32, "second request")
+                po += co
+                if po >= len(other):
+                    eng.end("o")
+            pos += c
+        for t in range(pos, n):
+            rows.append(eng.step([("p", [toks[t]], [0])], decode=True)[0])
+        check(np.concatenate(rows), want, C.PREC_FP32, "portions and decoding")
+    finally:
+        eng.close()
+
+
 # ------------------------------------------------------------------ GPU: entry points
 @gpu
 def test_greedy_generation_through_the_engine_and_its_scheduler():
