@@ -643,6 +643,13 @@ static void linrec_common(nvllm_handle* h, LinRecArgs* a, const LayerRun& r) {
 static int run_linrec(nvllm_handle* h, const LinRecArgs& a, double in_cols, int in_S) {
   const int T = a.T;
   const double hd = (double)a.H * a.dim, hv = (double)a.H * a.vdim, asz = dt_size(h->adt);
+  if (linrec_decode_fused_ok(a)) {
+    // one row per sequence: the three kernels as one launch; algorithmic bytes: the state in and out, the row's inputs, the read-out
+    ProfScope ps(h, NVLLM_K_RECUR, (double)a.n_seqs * hd * a.vdim * 8 + (double)T * (in_cols * 4 + hv * asz) + hd * a.rank * 4,
+                 4.0 * T * hv * a.dim + 2.0 * T * hd * a.rank, (double)T * in_cols * 4 * (in_S - 1));
+    LAUNCH(h, launch_linrec_decode(h->stream, h->adt, a));
+    return NVLLM_OK;
+  }
   {
     ProfScope ps(h, NVLLM_K_RECUR, (double)T * (in_cols * 4 + (3 * hd + hv) * 4) + hd * a.rank * 4, 2.0 * T * hd * a.rank,
                  (double)T * in_cols * 4 * (in_S - 1));
@@ -799,6 +806,14 @@ static int ffn_moe_relu2(nvllm_handle* h, const ListedLayer& y, Pending* p1, Pen
   Pending h1;
   if ((rc = run_gemm(h, w.xn, H, y.w1, T, ff, H, 1.f, w.ws_a, w.ws_a_floats, ff, &h1, TC5_EPI_RELU2, w.hbuf, ff, nullptr)))
     return rc;
+  // steps of <= 8 rows: the activation is built inside the down projection's GEMV (one launch less)
+  const char* gpre_env = getenv("NVLLM_GEMV_PRE");
+  if (h1.S > 0 && T <= 8 && !(gpre_env && atoi(gpre_env) == 0)) {
+    GemvPre ga{};
+    ga.mode = 2; ga.hp = h1.p; ga.Sh = h1.S; ga.hstride = h1.stride; ga.hld = ff; ga.swiglu = 2;
+    return run_gemm(h, w.hbuf, ff, y.w2, T, H, ff, 1.f, w.ws_b, w.ws_b_floats, H, p2, 0, nullptr, 0, nullptr, nullptr, 0,
+                    0.0, nullptr, nullptr, &ga);
+  }
   if (h1.S > 0) {
     ProfScope ps(h, NVLLM_K_ACT, (double)T * ff * (4 + asz), 0, (double)T * ff * 4 * (h1.S - 1));
     LAUNCH(h, launch_act(h->stream, h->adt, T, ff, h1.p, h1.S, h1.stride, nullptr, 2, w.hbuf));

@@ -518,6 +518,9 @@ struct LinRecArgs {
 cudaError_t launch_linrec_prep(cudaStream_t st, const LinRecArgs& a);
 cudaError_t launch_linrec_scan(cudaStream_t st, const LinRecArgs& a);
 cudaError_t launch_linrec_out(cudaStream_t st, int odt, const LinRecArgs& a);
+// One row per sequence (T == n_seqs) and vdim <= 128: prep + scan + out as one launch (a CTA per sequence and head)
+bool linrec_decode_fused_ok(const LinRecArgs& a);
+cudaError_t launch_linrec_decode(cudaStream_t st, int odt, const LinRecArgs& a);
 constexpr int LINREC_MAX_DIM = 256;
 // Token shift: out[s][t][:] = h_t + (h_{t-1} - h_t) * mu[s][:] for s < n_mix (act dtype, [n_mix][T][W]);
 // h_{t-1} of a step's first row comes from the sequence's slot (tail [W]), zeros at position 0.

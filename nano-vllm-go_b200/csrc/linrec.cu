@@ -20,6 +20,7 @@
 //                        partial read-outs meet in shared memory once per chunk.  State read from the slot
 //                        when the sequence has earlier tokens, written back at the end.
 //   linrec_out_kernel    per token, a warp per head: RMS over vdim, weight, silu(gate) -> act dtype.
+//   linrec_decode_kernel steps with one row per sequence (decode): the three kernels above as one launch per layer.
 //   token_shift_kernel   the inputs of time mixing's projections: h_t + (h_{t-1} - h_t) mu_s.
 //   roll_tails_kernel    after a step, the last inputs of a short convolution / token shift become
 //                        the slot's tail (one thread per channel reads all it needs, then writes).
@@ -165,11 +166,15 @@ cudaError_t launch_linrec_prep(cudaStream_t st, const LinRecArgs& a) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(linrec_prep_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     (void)launch_k(linrec_prep_kernel<16>, dim3(ceil_div(a.T, 16), std::min(4, ceil_div(big, 256))), dim3(256), smem, st, a,
                    next_trace(40));
-  } else {
+  } else if (a.T >= 512) {
     const size_t smem = (size_t)4 * rank_p * sizeof(float);
     if (smem > 48 * 1024) cudaFuncSetAttribute(linrec_prep_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     (void)launch_k(linrec_prep_kernel<4>, dim3(ceil_div(a.T, 4), std::min(8, ceil_div(big, 256))), dim3(256), smem, st, a,
                    next_trace(40));
+  } else {  // decode-sized steps: latency matters, not the matrix's trips through L2 — a CTA per token and 256 entries
+    const size_t smem = (size_t)rank_p * sizeof(float);
+    if (smem > 48 * 1024) cudaFuncSetAttribute(linrec_prep_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    (void)launch_k(linrec_prep_kernel<1>, dim3(a.T, std::min(16, ceil_div(big, 256))), dim3(256), smem, st, a, next_trace(40));
   }
   return cudaGetLastError();
 }
@@ -333,6 +338,189 @@ cudaError_t launch_linrec_scan(cudaStream_t st, const LinRecArgs& a) {
   if (a.dim <= 64) return linrec_scan_launch<16, 4>(st, a);
   if (a.dim <= 128) return linrec_scan_launch<32, 4>(st, a);
   return linrec_scan_launch<32, 8>(st, a);
+}
+
+// ------------------------------------------------------------------ one token per sequence: everything in one kernel
+// A decode step gives every sequence one row, and a head whose value columns fit one CTA
+// (vdim <= 32 CC) needs nothing from other CTAs: the projections' epilogue (split-K sums, the
+// decay), the state update with its read-out, the head's RMS norm, weight and gate run as ONE
+// launch per layer instead of three.  CTA = (sequence, head); the state slice of a thread is as
+// in linrec_scan_kernel and its loads are in flight while the row's inputs are prepared.
+template <int RPL, int NW, int CC, bool TMIX>
+__global__ void __launch_bounds__(32 * NW) linrec_decode_kernel(LinRecArgs a, int out_bf16, Trace tr) {
+  TRACE_ENTRY(tr);
+  pdl_launch_dependents();
+  constexpr int NT = 32 * NW;
+  constexpr int DP = RPL * NW;
+  constexpr int VC = 32 * CC;
+  extern __shared__ __align__(16) float sm[];
+  float* sq = sm;                 // [DP] q | [DP] k | [DP] decay
+  float* sv = sm + 3 * DP;        // [VC]
+  float* part = sv + VC;          // [NW][VC]
+  float* slr = part + NW * VC;    // [rank]
+  __shared__ float red[32];
+  const int t = blockIdx.x, head = blockIdx.y;
+  const int tid = threadIdx.x, l = tid >> 5, lane = tid & 31;
+  const int dim = a.dim, vdim = a.vdim;
+  pdl_wait();
+  const bool has_prev = a.positions[t] > 0;
+  float* state = a.state_pool + (size_t)a.state_slots[t] * a.slot_floats + a.state_off + (size_t)head * dim * vdim;
+  float S[CC][RPL], U[TMIX ? RPL : 1];
+#pragma unroll
+  for (int g = 0; g < RPL / 4; g++)
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+      const int r = (g * NW + l) * 4 + e;
+#pragma unroll
+      for (int cc = 0; cc < CC; cc++) {
+        const int col = cc * 32 + lane;
+        S[cc][g * 4 + e] = (r < dim && col < vdim && has_prev) ? state[(size_t)r * vdim + col] : 0.f;
+      }
+      if (TMIX) U[g * 4 + e] = r < dim ? a.bonus[head * dim + r] : 0.f;
+    }
+  for (int r = tid; r < a.rank; r += NT) {
+    const float x = seg_at(a.lr, t, r);
+    slr[r] = a.tmix ? tanhf(x) : x;
+  }
+  for (int c = tid; c < VC; c += NT) sv[c] = c < vdim ? seg_at(a.v, t, head * vdim + c) : 0.f;
+  __syncthreads();
+  const float inv_tau = 1.0f / a.tau;
+  for (int i = tid; i < DP; i += NT) {
+    float q = 0.f, k = 0.f, decay = 0.f;
+    if (i < dim) {
+      const int c = head * dim + i;
+      const float* w = a.w2 + (size_t)c * a.rank;
+      float z = 0.f;
+      if ((a.rank & 3) == 0) {  // 16-byte loads of the matrix row, four at a time in flight
+#pragma unroll 4
+        for (int r = 0; r < a.rank; r += 4) {
+          const float4 wv = *reinterpret_cast<const float4*>(w + r);
+          z = fmaf(wv.x, slr[r], z);
+          z = fmaf(wv.y, slr[r + 1], z);
+          z = fmaf(wv.z, slr[r + 2], z);
+          z = fmaf(wv.w, slr[r + 3], z);
+        }
+      } else {
+        for (int r = 0; r < a.rank; r++) z = fmaf(w[r], slr[r], z);
+      }
+      z += a.w2b[c];
+      if (a.tmix) {
+        decay = expf(-expf(z));
+      } else {
+        const float ls = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));  // log sigmoid(z)
+        decay = expf(ls * inv_tau);
+      }
+      q = seg_at(a.q, t, c);
+      k = seg_at(a.k, t, c);
+    }
+    sq[i] = q;
+    sq[DP + i] = k;
+    sq[2 * DP + i] = decay;
+  }
+  __syncthreads();
+  float v[CC], acc[CC];
+#pragma unroll
+  for (int cc = 0; cc < CC; cc++) {
+    v[cc] = sv[cc * 32 + lane];
+    acc[cc] = 0.f;
+  }
+#pragma unroll
+  for (int g = 0; g < RPL / 4; g++) {
+    const int rb = (g * NW + l) * 4;
+    const float4 q4 = *reinterpret_cast<const float4*>(sq + rb);
+    const float4 k4 = *reinterpret_cast<const float4*>(sq + DP + rb);
+    const float4 w4 = *reinterpret_cast<const float4*>(sq + 2 * DP + rb);
+    const float qq[4] = {q4.x, q4.y, q4.z, q4.w}, kk[4] = {k4.x, k4.y, k4.z, k4.w}, ww[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+#pragma unroll
+      for (int cc = 0; cc < CC; cc++) {
+        float& st = S[cc][g * 4 + e];
+        if (TMIX) {
+          const float kv = kk[e] * v[cc];
+          acc[cc] = fmaf(qq[e], fmaf(U[g * 4 + e], kv, st), acc[cc]);
+          st = fmaf(ww[e], st, kv);
+        } else {
+          st = fmaf(ww[e], st, kk[e] * v[cc]);
+          acc[cc] = fmaf(qq[e], st, acc[cc]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int cc = 0; cc < CC; cc++) part[l * VC + cc * 32 + lane] = acc[cc];
+#pragma unroll
+  for (int g = 0; g < RPL / 4; g++)
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+      const int r = (g * NW + l) * 4 + e;
+#pragma unroll
+      for (int cc = 0; cc < CC; cc++) {
+        const int col = cc * 32 + lane;
+        if (r < dim && col < vdim) state[(size_t)r * vdim + col] = S[cc][g * 4 + e];
+      }
+    }
+  __syncthreads();
+  // the head's read-out: a thread per column (NT >= 128 >= VC)
+  float o = 0.f, gt = 0.f, wn = 0.f;
+  const bool mine = tid < vdim;
+  if (mine) {
+#pragma unroll
+    for (int w = 0; w < NW; w++) o += part[w * VC + tid];
+    o *= a.qmul;
+    gt = seg_at(a.gate, t, head * vdim + tid);
+    wn = a.onorm_w[(size_t)head * a.onorm_ld + tid];
+  }
+  const float inv = 1.0f / sqrtf(block_sum(o * o, red) / (float)vdim + a.eps);
+  const float res = o * inv * wn * silu(gt);
+  if (out_bf16) {
+    bf16* out = (bf16*)a.out + (size_t)t * a.o_ld;
+    if (mine) out[head * vdim + tid] = __float2bfloat16_rn(res);
+    if (head == 0)
+      for (int c = a.H * vdim + tid; c < a.o_ld; c += NT) out[c] = __float2bfloat16_rn(0.f);
+  } else {
+    float* out = (float*)a.out + (size_t)t * a.o_ld;
+    if (mine) out[head * vdim + tid] = res;
+    if (head == 0)
+      for (int c = a.H * vdim + tid; c < a.o_ld; c += NT) out[c] = 0.f;
+  }
+  TRACE_EXIT(tr);
+}
+
+template <int RPL, int NW, int CC>
+static cudaError_t linrec_decode_launch_cc(cudaStream_t st, int odt, const LinRecArgs& a) {
+  const size_t smem = (size_t)(3 * RPL * NW + 32 * CC + NW * 32 * CC + a.rank) * sizeof(float);
+  const int bf = odt == DT_BF16;
+  if (a.tmix) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(linrec_decode_kernel<RPL, NW, CC, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    (void)launch_k(linrec_decode_kernel<RPL, NW, CC, true>, dim3(a.T, a.H), dim3(32 * NW), smem, st, a, bf, next_trace(45));
+  } else {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(linrec_decode_kernel<RPL, NW, CC, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    (void)launch_k(linrec_decode_kernel<RPL, NW, CC, false>, dim3(a.T, a.H), dim3(32 * NW), smem, st, a, bf, next_trace(45));
+  }
+  return cudaGetLastError();
+}
+template <int RPL, int NW>
+static cudaError_t linrec_decode_launch(cudaStream_t st, int odt, const LinRecArgs& a) {
+  if (a.vdim <= 32) return linrec_decode_launch_cc<RPL, NW, 1>(st, odt, a);
+  if (a.vdim <= 64) return linrec_decode_launch_cc<RPL, NW, 2>(st, odt, a);
+  return linrec_decode_launch_cc<RPL, NW, 4>(st, odt, a);
+}
+bool linrec_decode_fused_ok(const LinRecArgs& a) {
+  static const bool on = [] {
+    const char* e = getenv("NVLLM_LINREC_FUSED");
+    return e ? atoi(e) != 0 : true;
+  }();
+  return on && a.T == a.n_seqs && a.vdim <= 128 && a.dim <= LINREC_MAX_DIM;
+}
+cudaError_t launch_linrec_decode(cudaStream_t st, int odt, const LinRecArgs& a) {
+  if (a.T <= 0) return cudaSuccess;
+  if (!linrec_decode_fused_ok(a) || (a.tmix && !a.bonus)) return cudaErrorInvalidValue;
+  if (a.dim <= 16) return linrec_decode_launch<4, 4>(st, odt, a);
+  if (a.dim <= 32) return linrec_decode_launch<8, 4>(st, odt, a);
+  if (a.dim <= 64) return linrec_decode_launch<16, 4>(st, odt, a);
+  if (a.dim <= 128) return linrec_decode_launch<32, 4>(st, odt, a);
+  return linrec_decode_launch<32, 8>(st, odt, a);
 }
 
 // ------------------------------------------------------------------ gated norm of the read-out
