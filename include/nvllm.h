@@ -190,27 +190,35 @@ int nvllm_create(const nvllm_config* cfg, const uint8_t* tp_id, nvllm_handle** o
  *                                   the sublayers read x itself, the norm sits on their output (Zozonex)
  *   NVLLM_LBLOCK_SEQUENTIAL_PRENORM   x += mixer(RMSNorm(x)), then x += feed_forward(RMSNorm(x)); a run of
  *                                   layers may repeat with the same weights (loop_*), every pass with caches and
- *                                   state of its own and a learned vector added to x at its start       (Lazovik)
+ *                                   state of its own and a learned vector added to x at its start (Lazovik, Sutuvik)
  * Tensors are handed in by checkpoint name (nvllm_set_named_weight, or nvllm_load_safetensors
- * with NVLLM_ARCH_DUGOPEL / NVLLM_ARCH_ZOZONEX / NVLLM_ARCH_LAZOVIK). */
+ * with NVLLM_ARCH_DUGOPEL / NVLLM_ARCH_ZOZONEX / NVLLM_ARCH_LAZOVIK / NVLLM_ARCH_SUTUVIK). */
 enum nvllm_mixer_kind {
   NVLLM_MIXER_LATENT_ATTENTION = 1,
   NVLLM_MIXER_WINDOW_ATTENTION = 2, /* grouped-query attention over a sliding window of the paged K / V cache */
   NVLLM_MIXER_DELTA = 3,            /* gated delta rule: a recurrent dim x vdim state per head, kept per state slot */
   NVLLM_MIXER_GLA = 4,              /* gated linear attention: S <- diag(alpha) S + k v^T, o = S^T q, state per slot */
-  NVLLM_MIXER_ATTN_TMIX = 5         /* two mixers on one input, their outputs summed with two scales: grouped-query
+  NVLLM_MIXER_ATTN_TMIX = 5,        /* two mixers on one input, their outputs summed with two scales: grouped-query
                                        attention (short convolution, whole-row q / k norm, rotation, score cap, chunked
                                        mask, output gate) and time mixing with a token shift (heads2 x dim2) */
+  NVLLM_MIXER_ATTENTION = 6,        /* grouped-query attention over the whole cached prefix, every option a field of the
+                                       spec: per-head q / k norm (qk_norm 1 / 3), partial rotation of interleaved pairs with
+                                       piecewise frequency scaling, a query multiplier that grows with the position, a
+                                       multiplier per head, score cap, a bias linear in the distance, a sink of score 0 or a
+                                       learned one per head, values mixed with an earlier layer's, a gate per head */
+  NVLLM_MIXER_MAMBA2 = 7            /* Mamba-2: per head S <- exp(-exp(A_log) dt) S + dt B x^T (state x vdim), y = S^T C + D x,
+                                       gated by silu(z) and then normed in groups; state and convolution tail per state slot */
 };
 enum nvllm_mlp_kind { NVLLM_MLP_NONE = 0, NVLLM_MLP_DENSE = 1, NVLLM_MLP_MOE = 2 };
 enum nvllm_ffn_act {
   NVLLM_FFN_GLU_CLAMPED = 0, /* W_down (g sigmoid(1.702 g) (u + 1)), g / u clamped by `limit` */
-  NVLLM_FFN_RELU2 = 1        /* W_down relu(W_up h)^2 */
+  NVLLM_FFN_RELU2 = 1,       /* W_down relu(W_up h)^2 */
+  NVLLM_FFN_SWIGLU = 2       /* W_down (silu(W_gate h) * (W_up h)) */
 };
 enum nvllm_layered_block {
   NVLLM_LBLOCK_PARALLEL_PRENORM = 0,
   NVLLM_LBLOCK_SEQUENTIAL_POSTNORM = 1,
-  NVLLM_LBLOCK_SEQUENTIAL_PRENORM = 2 /* x += mixer(RMSNorm(x)), then x += feed_forward(RMSNorm(x)) (Lazovik) */
+  NVLLM_LBLOCK_SEQUENTIAL_PRENORM = 2 /* x += mixer(RMSNorm(x)), then x += feed_forward(RMSNorm(x)) (Lazovik, Sutuvik) */
 };
 enum nvllm_layered_position { NVLLM_LPOS_NONE = 0, NVLLM_LPOS_SINUSOIDAL = 1 };
 
@@ -257,6 +265,29 @@ typedef struct nvllm_layer_spec {
   int32_t route_sigmoid;   /* 1: scores are sigmoid(logits) instead of a softmax over the experts */
   int32_t weight_on_input; /* 1: the routing weight multiplies the expert's input instead of its output */
   int32_t shared_ff;       /* > 0: one more expert of this inner size runs for every token, times sigmoid(W_sg h) */
+  /* NVLLM_MIXER_ATTENTION (uses heads, kv_heads, dim, vdim, scale, softcap, sink, qk_norm, rot_base, rot_dims and
+   * rot_factor / rot_original / rot_fast / rot_slow) */
+  int32_t rot_pairs;       /* 1: entry 2i rotates with entry 2i + 1 (interleaved) instead of i with i + rot_dims / 2 */
+  int32_t rot_piecewise;   /* 1: frequency scaling by wavelength l = 2 pi / f: f kept where l < rot_original / rot_fast,
+                              f / rot_factor where l > rot_original / rot_slow, between them the blend
+                              (1 - s) f / rot_factor + s f with s = (rot_original / l - rot_slow) / (rot_fast - rot_slow);
+                              cos / sin are not rescaled */
+  float qtemp_coef;        /* > 0: q at position p times 1 + qtemp_coef * ln(floor((p + 1) / qtemp_every) + 1) */
+  int32_t qtemp_every;
+  int32_t head_temp;       /* 1: the scores of head h are multiplied by tensor "mix.temp"[h] */
+  float dist_slope;        /* > 0: score(i, j) -= 2^(-dist_slope (h + 1) / heads) * (i - j) for head h */
+  int32_t sink_learned;    /* 1 (with sink = 1): the sink's score is tensor "mix.sink"[h] instead of 0 */
+  int32_t v_mix;           /* 1: v <- (1 - l) v + l v_first, l = tensor "mix.vmix", v_first = the values the first such
+                              layer of the model computed for the same token (that layer keeps its own) */
+  int32_t head_gate;       /* 1: head h's output times sigmoid(W_g h)_h, one number per head */
+  /* NVLLM_MIXER_MAMBA2 (uses heads, vdim, conv) */
+  int32_t state;           /* entries of B_t / C_t: the state of a head is state x vdim */
+  int32_t ssm_groups;      /* head h reads B / C of group h / (heads / ssm_groups) */
+  int32_t norm_groups;     /* the gated read-out is RMS-normed in this many equal parts */
+  /* mixture of experts, further routing rules */
+  int32_t route_correction; /* 1: tensor "mlp.correction" [experts] is added to the scores for the CHOICE only */
+  int32_t group_top2;       /* 1: a group of experts scores as the sum of its two best choice scores (else its best) */
+  int32_t route_norm;       /* 1 (with route_sigmoid): the weights are the chosen scores divided by their sum (+ 1e-20) */
 } nvllm_layer_spec;
 
 typedef struct nvllm_layered_config {
@@ -276,6 +307,16 @@ typedef struct nvllm_layered_config {
    * [loop_times, hidden]: row t is added to x before pass t (also when loop_times is 1).  loop_times < 1 or an
    * empty range: no such run */
   int32_t loop_start, loop_stop, loop_times;
+  /* sequential pre-norm blocks, further options */
+  int32_t norm_groups;     /* > 1: every norm of the residual stream splits the row into this many equal parts, each
+                              divided by its own root mean square */
+  int32_t embed_norm;      /* 1: x = norm(embed[token]) with tensor "embed.norm" */
+  int32_t mixer_conv;      /* taps > 1: what a mixer reads is h + conv(h), a causal convolution over time per channel
+                              (tensor "l<i>.canon1" [width, taps], last column = the current token); the last taps - 1
+                              rows of h are part of the sequence's state slot */
+  int32_t side_dim;        /* > 0: after a layer's feed-forward x += rmsnorm(W_proj (gelu_tanh(W_gate x) * e)) * w with
+                              e = "side.embed"[token][layer * side_dim, (layer + 1) * side_dim) */
+  float logit_scale;       /* != 0: logits are multiplied by it */
 } nvllm_layered_config;
 
 int nvllm_create_layered(const nvllm_layered_config* cfg, const nvllm_layer_spec* layers,
@@ -320,7 +361,8 @@ enum nvllm_arch {
   NVLLM_ARCH_GRANITE_MOE = 3, /* GetGraniteMoEMapping: router + stacked expert tensors */
   NVLLM_ARCH_DUGOPEL = 4,     /* layered handle: every tensor of the file by its own name */
   NVLLM_ARCH_ZOZONEX = 5,     /* layered handle, likewise */
-  NVLLM_ARCH_LAZOVIK = 6      /* layered handle, likewise */
+  NVLLM_ARCH_LAZOVIK = 6,     /* layered handle, likewise */
+  NVLLM_ARCH_SUTUVIK = 7      /* layered handle, likewise */
 };
 
 /* Load every weight of the model straight from `model_dir` — model.safetensors, or the shards

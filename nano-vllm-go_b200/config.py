@@ -26,10 +26,11 @@ ACT_GELU, ACT_SWIGLU = 0, 1
 BLOCK_SEQUENTIAL, BLOCK_PARALLEL = 0, 1
 PREC_FP32, PREC_BF16 = 0, 1
 # enum nvllm_arch (checkpoint families of generic_loader.go:60-182)
-ARCH_GPT2, ARCH_FALCON, ARCH_LLAMA, ARCH_GRANITE_MOE, ARCH_DUGOPEL, ARCH_ZOZONEX, ARCH_LAZOVIK = 0, 1, 2, 3, 4, 5, 6
+ARCH_GPT2, ARCH_FALCON, ARCH_LLAMA, ARCH_GRANITE_MOE, ARCH_DUGOPEL, ARCH_ZOZONEX, ARCH_LAZOVIK, ARCH_SUTUVIK = 0, 1, 2, 3, 4, 5, 6, 7
 MIXER_LATENT_ATTENTION, MIXER_WINDOW_ATTENTION, MIXER_DELTA, MIXER_GLA, MIXER_ATTN_TMIX = 1, 2, 3, 4, 5
+MIXER_ATTENTION, MIXER_MAMBA2 = 6, 7
 MLP_NONE, MLP_DENSE, MLP_MOE = 0, 1, 2
-FFN_GLU_CLAMPED, FFN_RELU2 = 0, 1
+FFN_GLU_CLAMPED, FFN_RELU2, FFN_SWIGLU = 0, 1, 2
 LBLOCK_PARALLEL_PRENORM, LBLOCK_SEQUENTIAL_POSTNORM, LBLOCK_SEQUENTIAL_PRENORM = 0, 1, 2
 LPOS_NONE, LPOS_SINUSOIDAL = 0, 1
 DT_F32, DT_BF16, DT_F16 = 0, 1, 2
@@ -309,6 +310,12 @@ class CLayerSpec(ctypes.Structure):
         ("tau", ctypes.c_float), ("lowrank", ctypes.c_int32), ("heads2", ctypes.c_int32), ("dim2", ctypes.c_int32),
         ("mix_scale", ctypes.c_float), ("mix2_scale", ctypes.c_float),
         ("route_sigmoid", ctypes.c_int32), ("weight_on_input", ctypes.c_int32), ("shared_ff", ctypes.c_int32),
+        ("rot_pairs", ctypes.c_int32), ("rot_piecewise", ctypes.c_int32),
+        ("qtemp_coef", ctypes.c_float), ("qtemp_every", ctypes.c_int32), ("head_temp", ctypes.c_int32),
+        ("dist_slope", ctypes.c_float), ("sink_learned", ctypes.c_int32), ("v_mix", ctypes.c_int32),
+        ("head_gate", ctypes.c_int32),
+        ("state", ctypes.c_int32), ("ssm_groups", ctypes.c_int32), ("norm_groups", ctypes.c_int32),
+        ("route_correction", ctypes.c_int32), ("group_top2", ctypes.c_int32), ("route_norm", ctypes.c_int32),
     ]
 
 
@@ -325,6 +332,8 @@ class CLayeredConfig(ctypes.Structure):
         ("block_style", ctypes.c_int32), ("position", ctypes.c_int32), ("tied_head", ctypes.c_int32),
         ("norm_offset", ctypes.c_float), ("num_state_slots", ctypes.c_int32),
         ("loop_start", ctypes.c_int32), ("loop_stop", ctypes.c_int32), ("loop_times", ctypes.c_int32),
+        ("norm_groups", ctypes.c_int32), ("embed_norm", ctypes.c_int32), ("mixer_conv", ctypes.c_int32),
+        ("side_dim", ctypes.c_int32), ("logit_scale", ctypes.c_float),
     ]
 
 
@@ -374,6 +383,21 @@ class LayerSpec:
     route_sigmoid: int = 0
     weight_on_input: int = 0
     shared_ff: int = 0
+    rot_pairs: int = 0
+    rot_piecewise: int = 0
+    qtemp_coef: float = 0.0
+    qtemp_every: int = 0
+    head_temp: int = 0
+    dist_slope: float = 0.0
+    sink_learned: int = 0
+    v_mix: int = 0
+    head_gate: int = 0
+    state: int = 0
+    ssm_groups: int = 0
+    norm_groups: int = 0
+    route_correction: int = 0
+    group_top2: int = 0
+    route_norm: int = 0
 
     def to_c(self) -> CLayerSpec:
         c = CLayerSpec()
@@ -386,6 +410,8 @@ class LayerSpec:
         p = f"l{layer}."
         if self.mixer in (MIXER_GLA, MIXER_ATTN_TMIX):
             return self._prenorm_shapes(p, width)
+        if self.mixer in (MIXER_ATTENTION, MIXER_MAMBA2):
+            return self._prenorm2_shapes(p, width)
         if self.mixer == MIXER_WINDOW_ATTENTION:
             d = {p + "norm1": (width,), p + "mix.q": (self.heads * self.dim, width),
                  p + "mix.o": (width, self.heads * self.vdim)}
@@ -461,9 +487,46 @@ def _prenorm_shapes(self, p: str, width: int) -> dict:
 LayerSpec._prenorm_shapes = _prenorm_shapes
 
 
+def _prenorm2_shapes(self, p: str, width: int) -> dict:
+    """Attention with its options / Mamba-2, and the mixture of gated experts."""
+    d = {p + "norm1": (width,)}
+    m = p + "mix."
+    if self.mixer == MIXER_ATTENTION:
+        hv = self.heads * self.vdim
+        d.update({m + "q": (self.heads * self.dim, width), m + "k": (self.kv_heads * self.dim, width),
+                  m + "v": (self.kv_heads * self.vdim, width), m + "o": (width, hv)})
+        if self.qk_norm == 3:
+            d.update({m + "q.norm": (self.dim,), m + "k.norm": (self.dim,)})
+        if self.v_mix:
+            d[m + "vmix"] = ()
+        if self.sink_learned:
+            d[m + "sink"] = (self.heads,)
+        if self.head_temp:
+            d[m + "temp"] = (self.heads,)
+        if self.head_gate:
+            d[m + "g"] = (self.heads, width)
+    else:
+        inner, gn = self.heads * self.vdim, self.ssm_groups * self.state
+        d.update({m + "in": (2 * inner + 2 * gn + self.heads, width), m + "conv": (inner + 2 * gn, self.conv),
+                  m + "conv.b": (inner + 2 * gn,), m + "dt_bias": (self.heads,), m + "A_log": (self.heads,),
+                  m + "D": (self.heads,), m + "norm": (inner,), m + "o": (width, inner)})
+    if self.mlp == MLP_MOE:
+        d[p + "norm2"] = (width,)
+        d[p + "mlp.router"] = (self.experts, width)
+        if self.route_correction:
+            d[p + "mlp.correction"] = (self.experts,)
+        for e in range(self.experts):
+            d.update({f"{p}mlp.e{e}.gate": (self.ff, width), f"{p}mlp.e{e}.up": (self.ff, width),
+                      f"{p}mlp.e{e}.down": (width, self.ff)})
+    return d
+
+
+LayerSpec._prenorm2_shapes = _prenorm2_shapes
+
+
 @dataclass(frozen=True)
 class ListedModelConfig:
-    """A model whose config.json lists its layers (architectures "Dugopel", "Zozonex", "Lazovik")."""
+    """A model whose config.json lists its layers (architectures "Dugopel", "Zozonex", "Lazovik", "Sutuvik")."""
     name: str
     vocab_size: int
     hidden: int
@@ -480,6 +543,11 @@ class ListedModelConfig:
     loop_start: int = 0
     loop_stop: int = 0
     loop_times: int = 0   # >= 1 with loop_stop > loop_start: layers [start, stop) run that often in a row
+    norm_groups: int = 0  # > 1: the stream's norms work on that many equal parts of the row
+    embed_norm: bool = False
+    mixer_conv: int = 0   # taps of the causal convolution added to what every mixer reads
+    side_dim: int = 0     # entries of the per-layer token input
+    logit_scale: float = 0.0
 
     @property
     def has_loop(self) -> bool:
@@ -501,7 +569,8 @@ class ListedModelConfig:
     @property
     def needs_state_slots(self) -> bool:
         """True when some layer keeps recurrent state per sequence (delta rule)."""
-        return any(l.mixer in (MIXER_DELTA, MIXER_GLA, MIXER_ATTN_TMIX) for l in self.layers)
+        return self.mixer_conv > 1 or any(l.mixer in (MIXER_DELTA, MIXER_GLA, MIXER_ATTN_TMIX, MIXER_MAMBA2)
+                                          for l in self.layers)
 
     def tensor_shapes(self) -> dict:
         d = {"embed": (self.vocab_size, self.hidden), "final.norm": (self.hidden,)}
@@ -509,19 +578,29 @@ class ListedModelConfig:
             d["head"] = (self.vocab_size, self.hidden)
         if self.has_loop:
             d["loop.step"] = (self.loop_times, self.hidden)
+        if self.embed_norm:
+            d["embed.norm"] = (self.hidden,)
+        if self.side_dim > 0:
+            d["side.embed"] = (self.vocab_size, len(self.layers) * self.side_dim)
         for i, l in enumerate(self.layers):
             d.update(l.tensor_shapes(i, self.hidden))
+            if self.mixer_conv > 1:
+                d[f"l{i}.canon1"] = (self.hidden, self.mixer_conv)
+            if self.side_dim > 0:
+                d.update({f"l{i}.side.gate": (self.side_dim, self.hidden), f"l{i}.side.proj": (self.hidden, self.side_dim),
+                          f"l{i}.side.norm": (self.hidden,)})
         return d
 
     def matmul_params(self) -> int:
         shapes = self.tensor_shapes()
-        n = sum(s[0] * s[1] for k, s in shapes.items() if len(s) == 2 and not k.endswith(".conv"))
+        n = sum(s[0] * s[1] for k, s in shapes.items()
+                if len(s) == 2 and not k.endswith(".conv") and not k.endswith(".canon1") and k != "side.embed")
         return n - (0 if self.tied_head else self.vocab_size * self.hidden)
 
     def cache_bytes_per_token(self, bytes_per_el: int = 2) -> int:
         n = 0
         for l in (self.layers[i] for i in self.runs):
-            if l.mixer == MIXER_ATTN_TMIX:
+            if l.mixer in (MIXER_ATTN_TMIX, MIXER_ATTENTION):
                 n += l.kv_heads * (l.dim + l.vdim) * bytes_per_el
             elif l.mixer == MIXER_LATENT_ATTENTION and l.kv_from < 0:
                 n += (l.kv_rank + l.rot_dim) * bytes_per_el
@@ -539,6 +618,10 @@ class ListedModelConfig:
             elif l.mixer == MIXER_ATTN_TMIX:
                 n += 4 * (l.heads2 * l.dim2 * l.dim2 + self.hidden +
                           (l.conv - 1) * (l.heads * l.dim + l.kv_heads * (l.dim + l.vdim)))
+            elif l.mixer == MIXER_MAMBA2:
+                n += 4 * (l.heads * l.state * l.vdim + (l.conv - 1) * (l.heads * l.vdim + 2 * l.ssm_groups * l.state))
+            if self.mixer_conv > 1:
+                n += 4 * (self.mixer_conv - 1) * self.hidden
         return n
 
     def to_c(self, precision: int, num_kv_blocks: int = -1, max_num_seqs: int = 512,
@@ -552,6 +635,8 @@ class ListedModelConfig:
         c.block_style, c.position, c.tied_head = self.block_style, self.position, int(self.tied_head)
         c.norm_offset, c.num_state_slots = self.norm_offset, num_state_slots
         c.loop_start, c.loop_stop, c.loop_times = self.loop_start, self.loop_stop, self.loop_times
+        c.norm_groups, c.embed_norm, c.mixer_conv = self.norm_groups, int(self.embed_norm), self.mixer_conv
+        c.side_dim, c.logit_scale = self.side_dim, self.logit_scale
         specs = (CLayerSpec * len(self.layers))(*[l.to_c() for l in self.layers])
         return c, specs
 
@@ -677,6 +762,65 @@ def lazovik_from_json(j: dict, shapes: Optional[dict] = None) -> ListedModelConf
         loop_stop=int(lp.get("stop") or 0) if times >= 1 else 0, loop_times=times)
 
 
+# the distance bias of Sutuvik's first attention kind: head h of H has the slope 2^(-8 (h + 1) / H)
+SUTUVIK_SLOPE_EXPONENT = 8.0
+
+
+def _sutuvik_layer(i: int, lc: dict) -> LayerSpec:
+    m = lc["mixer"]
+    kind = lc.get("type")
+    if kind in ("attention", "attention_2"):
+        kw = dict(mixer=MIXER_ATTENTION, heads=int(m["heads"]), kv_heads=int(m["kv_heads"]), dim=int(m["dim"]),
+                  vdim=int(m["vdim"]), scale=float(m["scale"]), sink=1, v_mix=int(bool(m.get("v_mix"))))
+        if kind == "attention":
+            qt = m.get("q_temp") or {}
+            kw.update(qk_norm=3, dist_slope=SUTUVIK_SLOPE_EXPONENT, sink_learned=1, head_gate=1,
+                      qtemp_coef=float(qt.get("coef") or 0.0), qtemp_every=int(qt.get("every") or 0))
+        else:
+            rot = m.get("rot") or {}
+            sc = rot.get("scaling") or {}
+            kw.update(qk_norm=1, head_temp=1, softcap=float(m.get("softcap") or 0.0), rot_pairs=1,
+                      rot_dims=int(rot.get("dims") or 0), rot_base=float(rot.get("base") or 0.0))
+            if sc:
+                kw.update(rot_piecewise=1, rot_factor=float(sc["factor"]), rot_original=float(sc["original"]),
+                          rot_fast=float(sc["high"]), rot_slow=float(sc["low"]))
+    elif kind == "mamba2":
+        kw = dict(mixer=MIXER_MAMBA2, heads=int(m["heads"]), vdim=int(m["vdim"]), dim=int(m["state"]),
+                  state=int(m["state"]), ssm_groups=int(m["groups"]), norm_groups=int(m["norm_groups"]),
+                  conv=int(m["conv"]))
+    else:
+        raise ValueError(f"layer {i}: unknown layer type {kind!r}")
+    mlp = lc.get("mlp")
+    if mlp is None:
+        pass
+    elif mlp["kind"] == "moe":
+        r = mlp["router"]
+        g = r.get("groups") or {}
+        kw.update(mlp=MLP_MOE, act=FFN_SWIGLU, ff=int(mlp["expert"]["ff"]), experts=int(r["experts"]), top=int(r["top"]),
+                  groups=int(g.get("count") or 0), keep_groups=int(g.get("keep") or 0), route_sigmoid=1,
+                  route_correction=1, group_top2=1, route_norm=1)
+    else:
+        raise ValueError(f"layer {i}: unknown feed-forward kind {mlp['kind']!r}")
+    return LayerSpec(**kw)
+
+
+def sutuvik_from_json(j: dict) -> ListedModelConfig:
+    """config.json of the Sutuvik design: attention layers of two kinds and Mamba-2 layers in any
+    order, pre-norm blocks whose norms work on equal parts of the row, a short causal convolution
+    added to what every mixer reads, sigmoid-routed gated experts chosen within the best groups,
+    a per-layer token input after the feed-forward, a normed embedding, logits through the
+    embedding table times a constant."""
+    nm = j["norm"]
+    return ListedModelConfig(
+        name="sutuvik", vocab_size=int(j["vocab"]), hidden=int(j["width"]),
+        layers=tuple(_sutuvik_layer(i, lc) for i, lc in enumerate(j["layers"])),
+        norm_eps=float(nm["eps"]), arch=ARCH_SUTUVIK, block_style=LBLOCK_SEQUENTIAL_PRENORM, tied_head=True,
+        norm_groups=int(nm.get("groups") or 1), embed_norm=True,
+        mixer_conv=int((j.get("canon") or {}).get("taps") or 0),
+        side_dim=int((j.get("token_side") or {}).get("dim") or 0),
+        logit_scale=float(j.get("logit_scale") or 0.0))
+
+
 def safetensors_shapes(model_dir: str) -> dict:
     """Tensor name -> shape from the header of model.safetensors (8-byte little-endian length,
     then that many bytes of JSON)."""
@@ -690,7 +834,8 @@ def safetensors_shapes(model_dir: str) -> dict:
 
 
 # model registry: config.json "architecture" -> config builder
-ARCHITECTURES = {"Dugopel": dugopel_from_json, "Zozonex": zozonex_from_json, "Lazovik": lazovik_from_json}
+ARCHITECTURES = {"Dugopel": dugopel_from_json, "Zozonex": zozonex_from_json, "Lazovik": lazovik_from_json,
+                 "Sutuvik": sutuvik_from_json}
 # builders that also want the checkpoint's tensor shapes
 _WANTS_SHAPES = {"Lazovik"}
 

@@ -56,6 +56,15 @@ __device__ __forceinline__ float sum_slices(const float* __restrict__ p, int S, 
   for (int s = 0; s < S; s++) acc += p[(size_t)s * stride];
   return acc;
 }
+// slope of the distance bias of a head: the score of key j for the query at i loses slope * (i - j)
+__device__ __forceinline__ float head_slope(const WinAttnArgs& a, int head) {
+  return a.slope_exp > 0.f ? exp2f(-a.slope_exp * (float)(head + 1) / (float)a.H) : 0.f;
+}
+// score of the sink (a term of the softmax denominator without a key or a value): 0 or learned per head
+__device__ __forceinline__ float sink_score(const WinAttnArgs& a, int head) { return a.sink_w ? a.sink_w[head] : 0.f; }
+__device__ __forceinline__ const float* gate_row(const WinAttnArgs& a, size_t row, int head, int vdim) {
+  return a.gate ? a.gate + row * a.gate_ld + (a.gate_head ? head : head * vdim) : nullptr;
+}
 }  // namespace
 
 // ------------------------------------------------------------------ projection epilogue
@@ -71,16 +80,32 @@ __global__ void __launch_bounds__(256) winattn_prep_kernel(WinAttnArgs a, Trace 
   pdl_wait();
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  const int n_items = a.H + (a.own_kv ? 2 * a.G : 0);
+  const int n_qkv = a.H + (a.own_kv ? 2 * a.G : 0);
+  const int n_items = n_qkv + (a.gate_out ? 1 : 0);
   const float* row = a.in_p + (size_t)t * a.in_ld;
   const int slot = a.slots[t];
   const int blk = slot / KV_BLOCK, off = slot % KV_BLOCK;
+  const int rot = 2 * a.rot_half;
+  const float* cs = a.rot_half ? a.cosT + (size_t)t * a.rot_half : nullptr;
+  const float* sn = a.rot_half ? a.sinT + (size_t)t * a.rot_half : nullptr;
+  // what multiplies every query of the row: grows with the position in steps of qtemp_every
+  float qmul = 1.f;
+  if (a.qtemp_coef > 0.f && a.qtemp_every > 0)
+    qmul = 1.0f + a.qtemp_coef * logf((float)((a.positions[t] + 1) / a.qtemp_every) + 1.0f);
+  const float lam = a.vmix ? a.vmix[0] : 0.f;
   for (int it = blockIdx.y * nw + warp; it < n_items; it += gridDim.y * nw) {
+    if (it == n_qkv) {  // the heads' gates: sigmoid of the H columns after Q | K | V
+      const float* gp = row + (a.H + (a.own_kv ? a.G : 0)) * a.dim + (a.own_kv ? a.G : 0) * a.vdim;
+      for (int i = lane; i < a.H; i += 32)
+        a.gate_out[(size_t)t * a.H + i] = 1.0f / (1.0f + expf(-sum_slices(gp + i, a.in_S, a.in_stride)));
+      continue;
+    }
     int col, n, kind;  // 0 = query, 1 = key, 2 = value
     if (it < a.H) { kind = 0; n = a.dim; col = it * a.dim; }
     else if (it < a.H + a.G) { kind = 1; n = a.dim; col = a.H * a.dim + (it - a.H) * a.dim; }
     else { kind = 2; n = a.vdim; col = (a.H + a.G) * a.dim + (it - a.H - a.G) * a.vdim; }
-    const bool in_regs = n <= 32 * WP_MAXV;
+    // the rotation of (i, i + rot_half) pairs reaches across lanes: those heads take the second path
+    const bool in_regs = n <= 32 * WP_MAXV && !(rot > 0 && !a.rot_pairs && kind != 2);
     float v[WP_MAXV];
 #pragma unroll
     for (int c = 0; c < WP_MAXV; c++) v[c] = 0.f;
@@ -101,8 +126,12 @@ __global__ void __launch_bounds__(256) winattn_prep_kernel(WinAttnArgs a, Trace 
         ss += x * x;
       }
     }
+    // (a rotation leaves the sum of squares as it is: the norm's factor comes from the unrotated entries)
     float inv = 1.f;
     if (kind != 2 && a.qk_norm) inv = 1.0f / sqrtf(warp_sum(ss) / (float)n + a.eps);
+    if (kind == 0) inv *= qmul * (a.head_scale ? a.head_scale[it] : 1.f);
+    const float* nw_ = (kind == 2 || a.qk_norm != 3) ? nullptr : (kind == 0 ? a.qnorm_w : a.knorm_w);
+    float* vf = (kind == 2 && a.vfirst) ? a.vfirst + (size_t)t * a.G * a.vdim + (size_t)(it - a.H - a.G) * a.vdim : nullptr;
     QT* qd = nullptr;
     KT* kd = nullptr;
     if (kind == 0) qd = (QT*)a.q + (size_t)t * a.H * a.dim + col;
@@ -112,14 +141,38 @@ __global__ void __launch_bounds__(256) winattn_prep_kernel(WinAttnArgs a, Trace 
 #pragma unroll
       for (int c = 0; c < WP_MAXV; c++) {
         const int i = lane + 32 * c;
+        float x = v[c];
+        if (kind != 2 && rot > 0) {  // pairs (2i, 2i + 1) sit in neighbouring lanes
+          const float o = __shfl_xor_sync(0xffffffffu, x, 1);
+          if (i < rot && i < n) x = (i & 1) ? x * cs[i >> 1] + o * sn[i >> 1] : x * cs[i >> 1] - o * sn[i >> 1];
+        }
         if (i < n) {
-          if (qd) qd[i] = from_f32<QT>(v[c] * inv);
-          else kd[i] = from_f32<KT>(v[c] * inv);
+          x *= inv;
+          if (nw_) x *= nw_[i];
+          if (vf) {
+            if (a.vfirst_write) vf[i] = x;
+            else x = (1.0f - lam) * x + lam * vf[i];
+          }
+          if (qd) qd[i] = from_f32<QT>(x);
+          else kd[i] = from_f32<KT>(x);
         }
       }
     } else {
       for (int i = lane; i < n; i += 32) {
-        const float x = sum_slices(row + col + i, a.in_S, a.in_stride) * inv;
+        float x = sum_slices(row + col + i, a.in_S, a.in_stride);
+        if (kind != 2 && i < rot) {
+          const int ip = a.rot_pairs ? (i ^ 1) : (i < a.rot_half ? i + a.rot_half : i - a.rot_half);
+          const int f = a.rot_pairs ? (i >> 1) : (i < a.rot_half ? i : ip);
+          const bool first = a.rot_pairs ? !(i & 1) : i < a.rot_half;
+          const float o = sum_slices(row + col + ip, a.in_S, a.in_stride);
+          x = first ? x * cs[f] - o * sn[f] : x * cs[f] + o * sn[f];
+        }
+        x *= inv;
+        if (nw_) x *= nw_[i];
+        if (vf) {
+          if (a.vfirst_write) vf[i] = x;
+          else x = (1.0f - lam) * x + lam * vf[i];
+        }
         if (qd) qd[i] = from_f32<QT>(x);
         else kd[i] = from_f32<KT>(x);
       }
@@ -130,8 +183,9 @@ __global__ void __launch_bounds__(256) winattn_prep_kernel(WinAttnArgs a, Trace 
 
 cudaError_t launch_winattn_prep(cudaStream_t st, int qdt, int kvdt, const WinAttnArgs& a) {
   if (a.T <= 0) return cudaSuccess;
+  if (2 * a.rot_half > a.dim || (a.vfirst && !a.own_kv)) return cudaErrorInvalidValue;
   // few rows (decode): the heads of a row spread over several CTAs
-  const int n_items = a.H + (a.own_kv ? 2 * a.G : 0);
+  const int n_items = a.H + (a.own_kv ? 2 * a.G : 0) + (a.gate_out ? 1 : 0);
   const int ny = a.T >= 1024 ? 1 : ceil_div(n_items, 8);
   const dim3 grid(a.T, ny);
   const int big = std::max(a.dim, a.vdim);
@@ -329,7 +383,8 @@ __global__ void __launch_bounds__(256) winattn_kernel(WinAttnArgs a, Trace tr) {
   const int* bt = a.block_tables + (size_t)seq * a.max_blocks;
   const KT* kpool = (const KT*)a.kpool;
   const KT* vpool = (const KT*)a.vpool;
-  const float m0 = a.sink ? 0.f : -INFINITY, l0 = a.sink ? 1.f : 0.f;
+  const float m0 = a.sink ? sink_score(a, head) : -INFINITY, l0 = a.sink ? 1.f : 0.f;
+  const float slope = head_slope(a, head);
 
   for (int qb = 0; qb < nq; qb += WA_QS) {
     const int nqs = min(WA_QS, nq - qb);
@@ -375,6 +430,7 @@ __global__ void __launch_bounds__(256) winattn_kernel(WinAttnArgs a, Trace tr) {
           float d = 0.f;
           for (int i = 0; i < dim; i++) d = fmaf(qr[i], kr[i], d);
           s = a.softcap > 0.f ? cap_score<sizeof(QT) == 2>(d, a.softcap) : d;
+          s -= slope * (float)(qp - j);
         }
         const float cmax = warp_max(s);
         if (cmax == -INFINITY) continue;  // no key of this tile is visible to the query
@@ -403,11 +459,11 @@ __global__ void __launch_bounds__(256) winattn_kernel(WinAttnArgs a, Trace tr) {
       if (qi >= nqs) continue;
       const float inv = 1.0f / l[qq];
       QT* op = (QT*)a.out + (size_t)(row0 + qb + qi) * a.o_ld;
-      const float* gt = a.gate ? a.gate + (size_t)(row0 + qb + qi) * a.gate_ld + head * vdim : nullptr;
+      const float* gt = gate_row(a, (size_t)(row0 + qb + qi), head, vdim);
 #pragma unroll
       for (int c = 0; c < VPL; c++) {
         const int col = lane + 32 * c;
-        if (col < vdim) op[head * vdim + col] = from_f32<QT>(acc[qq][c] * inv * (gt ? gt[col] : 1.f));
+        if (col < vdim) op[head * vdim + col] = from_f32<QT>(acc[qq][c] * inv * (gt ? gt[a.gate_head ? 0 : col] : 1.f));
       }
       if (head == 0)  // padding columns of the output projection's input stay zero
         for (int col = a.H * vdim + lane; col < a.o_ld; col += 32) op[col] = from_f32<QT>(0.f);
@@ -457,6 +513,7 @@ __global__ void __launch_bounds__(128) winattn_decode_kernel(WinAttnArgs a, Trac
   const int g = head / (a.H / a.G);
   const int qp = a.seq_len[seq] - 1;
   const int k_lo = first_key(a, qp);
+  const float slope = head_slope(a, head);
   const int* bt = a.block_tables + (size_t)seq * a.max_blocks;
   const KT* kpool = (const KT*)a.kpool;
   const KT* vpool = (const KT*)a.vpool;
@@ -475,6 +532,7 @@ __global__ void __launch_bounds__(128) winattn_decode_kernel(WinAttnArgs a, Trac
       float d = 0.f;
       for (int i = 0; i < dim; i++) d = fmaf(qs[i], to_f32(kr[i]), d);
       s = a.softcap > 0.f ? cap_score<sizeof(QT) == 2>(d, a.softcap) : d;
+      s -= slope * (float)(qp - j);
     }
     const float mn = fmaxf(m, warp_max(s));  // lane 0 of the chunk is always visible
     const float corr = (m == -INFINITY) ? 0.f : expf(m - mn);
@@ -506,9 +564,10 @@ __global__ void __launch_bounds__(128) winattn_decode_kernel(WinAttnArgs a, Trac
     mine[vdim + 1] = l;
   }
   __syncthreads();
-  float mt = a.sink ? 0.f : -INFINITY;
+  const float sk = sink_score(a, head);
+  float mt = a.sink ? sk : -INFINITY;
   for (int w = 0; w < 4; w++) mt = fmaxf(mt, part[w * (vdim + 2) + vdim]);
-  float lt = a.sink ? expf(0.f - mt) : 0.f;
+  float lt = a.sink ? expf(sk - mt) : 0.f;
   float cw[4];
   for (int w = 0; w < 4; w++) {
     const float mw = part[w * (vdim + 2) + vdim];
@@ -519,7 +578,7 @@ __global__ void __launch_bounds__(128) winattn_decode_kernel(WinAttnArgs a, Trac
   for (int col = threadIdx.x; col < vdim; col += blockDim.x) {
     float v = 0.f;
     for (int w = 0; w < 4; w++) v += part[w * (vdim + 2) + col] * cw[w];
-    if (a.gate) v *= a.gate[(size_t)seq * a.gate_ld + head * vdim + col];
+    if (a.gate) v *= gate_row(a, (size_t)seq, head, vdim)[a.gate_head ? 0 : col];
     op[head * vdim + col] = from_f32<QT>(v / lt);
   }
   if (head == 0)
@@ -625,7 +684,9 @@ __global__ void __launch_bounds__(256, (GQMAX * VPT <= 16) ? 2 : 1) winattn_deco
     float p[GQMAX];
 #pragma unroll
     for (int q = 0; q < GQMAX; q++) {
-      const float sv = vis ? (a.softcap > 0.f ? cap_score<sizeof(QT) == 2>(s[q], a.softcap) : s[q]) : -INFINITY;
+      const float sv = vis ? (a.softcap > 0.f ? cap_score<sizeof(QT) == 2>(s[q], a.softcap) : s[q]) -
+                                 head_slope(a, h0 + q) * (float)(qp - j)
+                           : -INFINITY;
       const float mn = fmaxf(m[q], warp_max(sv));  // lane 0 of a chunk is always visible
       const float corr = (m[q] == -INFINITY) ? 0.f : expf(m[q] - mn);
       p[q] = vis ? expf(sv - mn) : 0.f;
@@ -670,16 +731,17 @@ __global__ void __launch_bounds__(256, (GQMAX * VPT <= 16) ? 2 : 1) winattn_deco
   __syncthreads();
   for (int i = threadIdx.x; i < gqn * vdim; i += blockDim.x) {
     const int q = i / vdim, col = i % vdim;
-    float mt = a.sink ? 0.f : -INFINITY;
+    const float sk = sink_score(a, h0 + q);
+    float mt = a.sink ? sk : -INFINITY;
     for (int w = 0; w < WD_WARPS; w++) mt = fmaxf(mt, part[((size_t)w * GQMAX + q) * ps + vdim]);
-    float lt = a.sink ? expf(0.f - mt) : 0.f, v = 0.f;
+    float lt = a.sink ? expf(sk - mt) : 0.f, v = 0.f;
     for (int w = 0; w < WD_WARPS; w++) {
       const float* pw = part + ((size_t)w * GQMAX + q) * ps;
       const float cw = (pw[vdim] == -INFINITY) ? 0.f : expf(pw[vdim] - mt);
       lt += pw[vdim + 1] * cw;
       v += pw[col] * cw;
     }
-    if (a.gate) v *= a.gate[(size_t)seq * a.gate_ld + (size_t)(h0 + q) * vdim + col];
+    if (a.gate) v *= gate_row(a, (size_t)seq, h0 + q, vdim)[a.gate_head ? 0 : col];
     ((QT*)a.out)[(size_t)seq * a.o_ld + (size_t)(h0 + q) * vdim + col] = from_f32<QT>(v / lt);
   }
   if (g == 0 && blockIdx.z == 0)
@@ -813,8 +875,9 @@ __global__ void __launch_bounds__(128) winattn_mma_kernel(WinAttnArgs a, Trace t
   const int r_lo = warp * 16 + gid, r_hi = r_lo + 8;     // the thread's two query rows in the tile
   const int qp_lo = qpos0 + r_lo, qp_hi = qpos0 + r_hi;  // their positions
   float m_lo, m_hi, l_lo, l_hi;
-  m_lo = m_hi = a.sink ? 0.f : -INFINITY;
+  m_lo = m_hi = a.sink ? sink_score(a, head) * 1.4426950408889634f : -INFINITY;  // base-2 domain, like the scores
   l_lo = l_hi = a.sink ? 1.f : 0.f;
+  const float slope2 = head_slope(a, head) * 1.4426950408889634f;
   float o[VDIM / 8][4];
 #pragma unroll
   for (int i = 0; i < VDIM / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
@@ -866,6 +929,11 @@ __global__ void __launch_bounds__(128) winattn_mma_kernel(WinAttnArgs a, Trace t
 #pragma unroll
         for (int nb = 0; nb < WM_K / 8; nb++) {
           s[nb][0] *= sc; s[nb][1] *= sc; s[nb][2] *= sc; s[nb][3] *= sc;
+          if (slope2 != 0.f) {
+            const int j = k0 + nb * 8 + tig * 2;
+            s[nb][0] -= slope2 * (float)(qp_lo - j); s[nb][1] -= slope2 * (float)(qp_lo - j - 1);
+            s[nb][2] -= slope2 * (float)(qp_hi - j); s[nb][3] -= slope2 * (float)(qp_hi - j - 1);
+          }
           mx_lo = fmaxf(mx_lo, fmaxf(s[nb][0], s[nb][1]));
           mx_hi = fmaxf(mx_hi, fmaxf(s[nb][2], s[nb][3]));
         }
@@ -877,7 +945,7 @@ __global__ void __launch_bounds__(128) winattn_mma_kernel(WinAttnArgs a, Trace t
             const int j = k0 + nb * 8 + tig * 2 + (e & 1);
             const int qp = (e & 2) ? qp_hi : qp_lo;
             const bool vis = j <= qp && j < k_hi && j >= first_key(a, qp);
-            const float v = vis ? s[nb][e] * sc : -INFINITY;
+            const float v = vis ? s[nb][e] * sc - slope2 * (float)(qp - j) : -INFINITY;
             s[nb][e] = v;
             if (e & 2) mx_hi = fmaxf(mx_hi, v);
             else mx_lo = fmaxf(mx_lo, v);
@@ -936,12 +1004,15 @@ __global__ void __launch_bounds__(128) winattn_mma_kernel(WinAttnArgs a, Trace t
   cp_async_wait<0>();
   const float i_lo = 1.0f / l_lo, i_hi = 1.0f / l_hi;
   bf16* ob = (bf16*)a.out + (size_t)row0 * a.o_ld + head * VDIM;
-  const float* gb = a.gate ? a.gate + (size_t)row0 * a.gate_ld + head * VDIM : nullptr;
+  const float* gb = gate_row(a, (size_t)row0, head, VDIM);
 #pragma unroll
   for (int i = 0; i < VDIM / 8; i++) {
     const int col = i * 8 + tig * 2;
     float g0 = 1.f, g1 = 1.f, g2 = 1.f, g3 = 1.f;
-    if (gb) {
+    if (gb && a.gate_head) {
+      if (r_lo < nq) g0 = g1 = gb[(size_t)r_lo * a.gate_ld];
+      if (r_hi < nq) g2 = g3 = gb[(size_t)r_hi * a.gate_ld];
+    } else if (gb) {
       if (r_lo < nq) { g0 = gb[(size_t)r_lo * a.gate_ld + col]; g1 = gb[(size_t)r_lo * a.gate_ld + col + 1]; }
       if (r_hi < nq) { g2 = gb[(size_t)r_hi * a.gate_ld + col]; g3 = gb[(size_t)r_hi * a.gate_ld + col + 1]; }
     }
@@ -1023,6 +1094,9 @@ __global__ void __launch_bounds__(128) winattn_decode_mma_kernel(WinAttnArgs a, 
   for (int i = 0; i < VDIM / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   uint32_t qa[DIM / 16][4];
   const float sc = a.scale * 1.4426950408889634f;  // log2(e): softmax in base 2
+  // the thread's two rows are two heads of the group, each with its own slope
+  const float slope_lo = gid < GQ ? head_slope(a, h0 + gid) * 1.4426950408889634f : 0.f;
+  const float slope_hi = gid + 8 < GQ ? head_slope(a, h0 + gid + 8) * 1.4426950408889634f : 0.f;
 
   for (int kt = 0; kt < n_kt; kt++) {
     if (kt + 2 < n_kt) load_kv(kt + 2);
@@ -1055,7 +1129,8 @@ __global__ void __launch_bounds__(128) winattn_decode_mma_kernel(WinAttnArgs a, 
 #pragma unroll
         for (int e = 0; e < 4; e++) {
           const int j = j0 + nb * 8 + tig * 2 + (e & 1);
-          const float sv = a.softcap > 0.f ? cap_score<true>(s[nb][e] * a.scale, a.softcap) * 1.4426950408889634f : s[nb][e] * sc;
+          const float sv = (a.softcap > 0.f ? cap_score<true>(s[nb][e] * a.scale, a.softcap) * 1.4426950408889634f : s[nb][e] * sc) -
+                           ((e & 2) ? slope_hi : slope_lo) * (float)(qp - j);
           const float v = (j >= k_lo && j <= qp) ? sv : -INFINITY;  // every row sits at position qp
           s[nb][e] = v;
           if (e & 2) mx_hi = fmaxf(mx_hi, v);
@@ -1124,16 +1199,17 @@ __global__ void __launch_bounds__(128) winattn_decode_mma_kernel(WinAttnArgs a, 
   __syncthreads();
   for (int i = threadIdx.x; i < GQ * VDIM; i += blockDim.x) {
     const int r = i / VDIM, col = i % VDIM;
-    float mt = a.sink ? 0.f : -INFINITY;
+    const float sk = sink_score(a, h0 + r) * 1.4426950408889634f;
+    float mt = a.sink ? sk : -INFINITY;
     for (int w = 0; w < 4; w++) mt = fmaxf(mt, mrg[((size_t)w * 16 + r) * MS + VDIM]);
-    float lt = a.sink ? exp2f(0.f - mt) : 0.f, v = 0.f;
+    float lt = a.sink ? exp2f(sk - mt) : 0.f, v = 0.f;
     for (int w = 0; w < 4; w++) {
       const float* pw = mrg + ((size_t)w * 16 + r) * MS;
       const float cw = exp2f(pw[VDIM] - mt);  // a warp that saw no key has max -inf: weight 0
       lt += pw[VDIM + 1] * cw;
       v += pw[col] * cw;
     }
-    if (a.gate) v *= a.gate[(size_t)seq * a.gate_ld + (size_t)(h0 + r) * VDIM + col];
+    if (a.gate) v *= gate_row(a, (size_t)seq, h0 + r, VDIM)[a.gate_head ? 0 : col];
     ((bf16*)a.out)[(size_t)seq * a.o_ld + (size_t)(h0 + r) * VDIM + col] = __float2bfloat16_rn(v / lt);
   }
   if (g == 0)

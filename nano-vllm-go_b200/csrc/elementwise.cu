@@ -106,7 +106,7 @@ __global__ void __launch_bounds__(512) norm_kernel(NormArgs a, Trace tr) {
 #pragma unroll
   for (int j = 0; j < 8; j++) w0[j] = b0[j] = bias1_0[j] = bias2_0[j] = 0.f;
   if (i0 < H) {
-    if (a.y || a.post) {
+    if (a.y || a.y_f32 || a.post) {
       if (a.w) load8(a.w + i0, w0);
       else
 #pragma unroll
@@ -236,10 +236,54 @@ __global__ void __launch_bounds__(512) norm_kernel(NormArgs a, Trace tr) {
       for (int j = 0; j < 8; j++) lsum += v[j] * v[j];
     }
   }
-  if (a.y == nullptr) return;
-  const unsigned long long t_loads = tr.buf ? gtime() : 0ull;
+  if (a.y == nullptr && a.y_f32 == nullptr) return;
+  if (a.plain) {  // no norm: the updated row itself goes out (each thread reads back what it staged)
+    YT* yp = (YT*)a.y + (size_t)orow * H;
+    for (int i = i0; i < H; i += blockDim.x * 8) {
+      float o[8];
+      load8(row + i, o);
+      store8(yp + i, o);
+    }
+    if (threadIdx.x == 0 && trace_on(tr)) trace_rec(tr, t_entry, t_wait, 0ull);
+    return;
+  }
+  unsigned long long t_loads = 0ull, t_red = 0ull;
+  if (a.groups > 1 && !ln) {
+    // RMS norm in equal parts: a warp sums the squares of one part at a time
+    __shared__ float ginv[64];
+    __syncthreads();
+    const int part = H / a.groups;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    for (int g = warp; g < a.groups; g += nw) {
+      float sq = 0.f;
+      for (int i = lane; i < part; i += 32) {
+        const float v = row[g * part + i];
+        sq = fmaf(v, v, sq);
+      }
+      sq = warp_sum(sq);
+      if (lane == 0) ginv[g] = 1.0f / sqrtf(sq / (float)part + a.eps);
+    }
+    __syncthreads();
+    YT* yg = a.y ? (YT*)a.y + (size_t)orow * H : nullptr;
+    for (int i = i0; i < H; i += blockDim.x * 8) {
+      float w[8], o[8];
+      if (i == i0) {
+#pragma unroll
+        for (int j = 0; j < 8; j++) w[j] = w0[j];
+      } else if (a.w) load8(a.w + i, w);
+      else
+#pragma unroll
+        for (int j = 0; j < 8; j++) w[j] = 1.f;
+#pragma unroll
+      for (int j = 0; j < 8; j++) o[j] = row[i + j] * ginv[(i + j) / part] * w[j];
+      if (yg) store8(yg + i, o);
+      if (a.y_f32) store8(a.y_f32 + (size_t)orow * H + i, o);
+      if (a.router || a.gate_w) store8(row + i, o);
+    }
+  } else {
+  t_loads = tr.buf ? gtime() : 0ull;
   float tot = block_sum(lsum, red);
-  const unsigned long long t_red = tr.buf ? gtime() : 0ull;
+  t_red = tr.buf ? gtime() : 0ull;
   float mean = 0.f, inv;
   if (ln) {
     mean = tot / (float)H;
@@ -256,7 +300,7 @@ __global__ void __launch_bounds__(512) norm_kernel(NormArgs a, Trace tr) {
   } else {
     inv = 1.0f / sqrtf(tot / (float)H + a.eps);
   }
-  YT* yr = (YT*)a.y + (size_t)orow * H;
+  YT* yr = a.y ? (YT*)a.y + (size_t)orow * H : nullptr;
   for (int i = i0; i < H; i += blockDim.x * 8) {
     float w[8], bb[8], o[8];
     if (i == i0) {
@@ -282,9 +326,10 @@ __global__ void __launch_bounds__(512) norm_kernel(NormArgs a, Trace tr) {
 #pragma unroll
       for (int j = 0; j < 8; j++) o[j] = row[i + j] * inv * w[j];
     }
-    store8(yr + i, o);
+    if (yr) store8(yr + i, o);
     if (a.y_f32) store8(a.y_f32 + (size_t)orow * H + i, o);
     if (a.router || a.gate_w) store8(row + i, o);  // each thread overwrites only what it alone reads
+  }
   }
   if (a.gate_w) {  // one number per token: sigmoid(normed row . gate_w), fp32
     float d = 0.f;
@@ -308,6 +353,7 @@ __global__ void __launch_bounds__(512) norm_kernel(NormArgs a, Trace tr) {
 
 cudaError_t launch_norm(cudaStream_t st, const NormArgs& a) {
   if (a.n_rows <= 0) return cudaSuccess;
+  if (a.groups > 64 || (a.groups > 1 && a.H % a.groups) || (a.plain && !a.y)) return cudaErrorInvalidValue;
   int threads = min(512, max(64, ((a.H / 8 + 31) / 32) * 32));
   // fused router, decode-sized batches (latency-bound: fewer row CTAs than two waves): 16 warps
   // so that each takes two experts of a 32-expert layer in one pass; prefill keeps the
@@ -392,6 +438,45 @@ cudaError_t launch_act(cudaStream_t st, int odt, int T, int F, const float* h, i
     (void)launch_k(act_kernel<float>, dim3(blocks), dim3(threads), 0, st, T, F, h, S, stride, bias, swiglu, (float*)out, glu_limit, next_trace(6));
   else
     (void)launch_k(act_kernel<bf16>, dim3(blocks), dim3(threads), 0, st, T, F, h, S, stride, bias, swiglu, (bf16*)out, glu_limit, next_trace(6));
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------- per-layer token input
+// g[t, j] = gelu_tanh(W_gate x)[t, j] * table[token[t]][col0 + j]: the split-K slices of the gate
+// projection summed, the activation in fp32, the token's entries of the layer's part of the table
+template <typename OT, typename WT>
+__global__ void token_gate_kernel(int T, int n, const float* __restrict__ h, int S, size_t stride, int ld_h,
+                                  const int* __restrict__ tokens, const WT* __restrict__ table, int ld_table, int col0,
+                                  OT* __restrict__ out, int ld_out, Trace tr) {
+  TRACE_ENTRY(tr);
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t total = (size_t)T * ld_out;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int t = (int)(i / ld_out), j = (int)(i % ld_out);
+    float o = 0.f;
+    if (j < n) {
+      float z = 0.f;
+      for (int s = 0; s < S; s++) z += h[(size_t)s * stride + (size_t)t * ld_h + j];
+      o = gelu_tanh(z) * to_f32(table[(size_t)tokens[t] * ld_table + col0 + j]);
+    }
+    out[i] = from_f32<OT>(o);
+  }
+  TRACE_EXIT(tr);
+}
+
+cudaError_t launch_token_gate(cudaStream_t st, int odt, int wdt, int T, int n, const float* h, int S, size_t stride, int ld_h,
+                              const int* tokens, const void* table, int ld_table, int col0, void* out, int ld_out) {
+  if (T <= 0) return cudaSuccess;
+  const size_t total = (size_t)T * ld_out;
+  const int blocks = (int)min((size_t)148 * 16, (total + 255) / 256);
+  if (odt == DT_F32 && wdt == DT_F32)
+    (void)launch_k(token_gate_kernel<float, float>, dim3(blocks), dim3(256), 0, st, T, n, h, S, stride, ld_h, tokens,
+                   (const float*)table, ld_table, col0, (float*)out, ld_out, next_trace(6));
+  else if (odt == DT_BF16 && wdt == DT_BF16)
+    (void)launch_k(token_gate_kernel<bf16, bf16>, dim3(blocks), dim3(256), 0, st, T, n, h, S, stride, ld_h, tokens,
+                   (const bf16*)table, ld_table, col0, (bf16*)out, ld_out, next_trace(6));
+  else return cudaErrorInvalidValue;
   return cudaGetLastError();
 }
 

@@ -27,7 +27,8 @@ void free_workspace(nvllm_handle* h) {
                   w.xb, w.ssq, w.chain_ctr, w.lat_cq, w.lat_gate, w.lat_o, w.dl_qkv, w.dl_bg, w.dl_o, w.m_xbc, w.m_dt, w.m_y, w.m_yn, w.logits_p, w.logits, w.attn_ws, w.out_tokens, w.amax, w.amax_ticket, w.topk_idx, w.topk_w,
                   w.sort.counts, w.sort.offsets, w.sort.cursor, w.sort.sorted_pair, w.sort.pair_row,
                   w.sort.a_rows, w.sort.tile_expert, w.sort.tile_row0, w.sort.tile_rows,
-                  w.sort.n_tiles, w.moe_Y, w.moe_y, w.moe_xs, w.lr_qkw, w.lr_v, w.lr_o, w.att_gate, w.sh_gate, w.mx_in};
+                  w.sort.n_tiles, w.moe_Y, w.moe_y, w.moe_xs, w.lr_qkw, w.lr_v, w.lr_o, w.att_gate, w.sh_gate, w.mx_in,
+                  w.m2_xbc, w.m2_dtx, w.m2_decay, w.v_first, w.side_g};
   for (void* p : ptrs)
     if (p) cudaFree(p);
   for (auto& r : h->ropes) {
@@ -116,11 +117,19 @@ int ensure_workspace(nvllm_handle* h, int T, int n) {
     WS(w.dl_qkv, Tc * dch * 4);
     WS(w.dl_bg, Tc * 2 * dh * 4);
     WS(w.dl_o, Tc * dhv * 4);
-    size_t lhd = 0, lhv = 0, agate = 0;
+    size_t lhd = 0, lhv = 0, agate = 0, m2ch = 0, m2in = 0, m2h = 0, vfirst = 0;
     bool tmix = false, shared = false;
     for (auto& y : h->ll) {
       const nvllm_layer_spec& s = y.s;
-      if (s.mixer == NVLLM_MIXER_GLA) {
+      if (s.mixer == NVLLM_MIXER_MAMBA2) {
+        lhv = std::max(lhv, (size_t)s.heads * s.vdim);
+        m2ch = std::max(m2ch, (size_t)y.conv_ch);
+        m2in = std::max(m2in, (size_t)s.heads * s.vdim);
+        m2h = std::max(m2h, (size_t)s.heads);
+      } else if (s.mixer == NVLLM_MIXER_ATTENTION) {
+        if (s.head_gate) agate = std::max(agate, (size_t)s.heads);
+        if (s.v_mix) vfirst = std::max(vfirst, (size_t)s.kv_heads * s.vdim);
+      } else if (s.mixer == NVLLM_MIXER_GLA) {
         lhd = std::max(lhd, (size_t)s.heads * s.dim);
         lhv = std::max(lhv, (size_t)s.heads * s.vdim);
       } else if (s.mixer == NVLLM_MIXER_ATTN_TMIX) {
@@ -135,6 +144,12 @@ int ensure_workspace(nvllm_handle* h, int T, int n) {
     WS(w.lr_v, Tc * lhv * 4);
     WS(w.lr_o, Tc * lhv * 4);
     WS(w.att_gate, Tc * agate * 4);
+    WS(w.m2_xbc, Tc * m2ch * 4);
+    WS(w.m2_dtx, Tc * m2in * 4);
+    WS(w.m2_decay, Tc * m2h * 4);
+    WS(w.v_first, Tc * vfirst * 4);
+    WS(w.side_g, Tc * (size_t)h->side_p * asz);
+    if (h->mixer_conv && !h->moe) WS(w.xn_f32, Tc * H * 4);
     if (tmix) WS(w.mx_in, (size_t)5 * Tc * H * asz);
     if (shared) WS(w.sh_gate, (size_t)Tc * 4);
     for (auto& r : h->ropes) {

@@ -48,7 +48,13 @@ void layered_free(nvllm_handle* h) {
     F(y.post1_w); F(y.post2_w); F(y.conv_w); F(y.a_log); F(y.dt_bias); F(y.onorm_w);
     F(y.bias_in); F(y.o_bias); F(y.qnorm_w); F(y.knorm_w); F(y.lr_w2); F(y.lr_b); F(y.mu); F(y.bonus);
     F(y.w_in2); F(y.w_o2); F(y.sh_gate);
+    F(y.sink_w); F(y.head_temp); F(y.vmix); F(y.conv_b); F(y.d_skip); F(y.route_corr); F(y.canon_w);
+    F(y.side_gate); F(y.side_proj); F(y.side_norm);
   }
+  F(h->embed_norm_w);
+  h->embed_norm_w = nullptr;
+  F(h->side_embed);
+  h->side_embed = nullptr;
   h->runs.clear();
   F(h->loop_step);
   h->loop_step = nullptr;
@@ -100,7 +106,12 @@ int layered_set_weight(nvllm_handle* h, const char* cname, int dtype, const void
                        const int64_t* shape, int ndim) {
   if (!h->layered) return set_err(h, NVLLM_ERR_STATE, "named weights belong to handles of nvllm_create_layered");
   if (h->finalized) return set_err(h, NVLLM_ERR_STATE, "set_named_weight after finalize");
-  if (!cname || !host || !shape || ndim < 1 || ndim > 2) return set_err(h, NVLLM_ERR_INVALID, "bad named weight");
+  if (!cname || !host || (!shape && ndim > 0) || ndim < 0 || ndim > 2) return set_err(h, NVLLM_ERR_INVALID, "bad named weight");
+  const int64_t one_el = 1;
+  if (ndim == 0) {  // a single number: handled as a vector of one
+    shape = &one_el;
+    ndim = 1;
+  }
   if (dtype < 0 || dtype > 2) return set_err(h, NVLLM_ERR_INVALID, "bad dtype %d", dtype);
   NV_CHECK(h, cudaSetDevice(h->dev));
   const std::string name(cname);
@@ -118,9 +129,59 @@ int layered_set_weight(nvllm_handle* h, const char* cname, int dtype, const void
   if (name == "embed") mat(h->wte, h->V, W, W);
   else if (name == "head" && h->lm_head_owned) mat(h->lm_head, h->V, W, W);
   else if (name == "final.norm") { vec(h->lnf_w, W); d.add = noff; }
+  else if (name == "embed.norm" && h->embed_norm_w) vec(h->embed_norm_w, W);
+  else if (name == "side.embed" && h->side_embed) mat(h->side_embed, h->V, (int64_t)h->L * h->side_dim, h->L * h->side_dim);
   else if (name == "loop.step" && h->loop_step) {
     mat(h->loop_step, h->loop_times, W, W);
     d.ddt = DT_F32; d.p = h->loop_step;
+  } else if (parse_layer_name(name, &l, &rest) && l < h->L &&
+             (h->ll[l].s.mixer == NVLLM_MIXER_ATTENTION || h->ll[l].s.mixer == NVLLM_MIXER_MAMBA2)) {
+    // sequential pre-norm blocks: attention with options / Mamba-2, mixture of gated experts, the
+    // convolution on the mixer's input and the per-layer token input
+    ListedLayer& y = h->ll[l];
+    const nvllm_layer_spec& s = y.s;
+    auto f32mat = [&](float* p, int64_t rows, int64_t cols) { mat(p, rows, cols, (int)cols); d.ddt = DT_F32; d.p = p; };
+    const int hv = s.heads * s.vdim;
+    if (rest == "norm1") vec(y.post1_w, W);
+    else if (rest == "norm2" && s.mlp != NVLLM_MLP_NONE) vec(y.post2_w, W);
+    else if (rest == "canon1" && y.canon_w) f32mat(y.canon_w, W, h->mixer_conv);
+    else if (rest == "side.gate" && y.side_gate) mat(y.side_gate, h->side_dim, W, W);
+    else if (rest == "side.proj" && y.side_proj) mat(y.side_proj, W, h->side_dim, h->side_p);
+    else if (rest == "side.norm" && y.side_norm) vec(y.side_norm, W);
+    else if (rest == "mix.o") mat(y.w_o, W, hv, y.ov_p);
+    else if (s.mixer == NVLLM_MIXER_ATTENTION) {
+      if (rest == "mix.q") mat(y.w_in, y.n_q, W, W, 0);
+      else if (rest == "mix.k") mat(y.w_in, y.n_k, W, W, y.n_q);
+      else if (rest == "mix.v") mat(y.w_in, y.n_v, W, W, y.n_q + y.n_k);
+      else if (rest == "mix.g" && s.head_gate) mat(y.w_in, s.heads, W, W, y.n_q + y.n_k + y.n_v);
+      else if (rest == "mix.q.norm" && s.qk_norm == 3) vec(y.qnorm_w, s.dim);
+      else if (rest == "mix.k.norm" && s.qk_norm == 3) vec(y.knorm_w, s.dim);
+      else if (rest == "mix.vmix" && s.v_mix) vec(y.vmix, 1);
+      else if (rest == "mix.sink" && s.sink_learned) vec(y.sink_w, s.heads);
+      else if (rest == "mix.temp" && s.head_temp) vec(y.head_temp, s.heads);
+    } else {
+      if (rest == "mix.in") mat(y.w_in, y.n_in, W, W);
+      else if (rest == "mix.conv") f32mat(y.conv_w, y.conv_ch, s.conv);
+      else if (rest == "mix.conv.b") vec(y.conv_b, y.conv_ch);
+      else if (rest == "mix.dt_bias") vec(y.dt_bias, s.heads);
+      else if (rest == "mix.A_log") vec(y.a_log, s.heads);
+      else if (rest == "mix.D") vec(y.d_skip, s.heads);
+      else if (rest == "mix.norm") vec(y.onorm_w, hv);
+    }
+    if (!d.p && s.mlp == NVLLM_MLP_MOE) {
+      if (rest == "mlp.router") f32mat(y.router, s.experts, W);
+      else if (rest == "mlp.correction" && s.route_correction) vec(y.route_corr, s.experts);
+      else if (rest.compare(0, 5, "mlp.e") == 0) {
+        size_t i = 5;
+        int e = 0;
+        while (i < rest.size() && rest[i] >= '0' && rest[i] <= '9') e = e * 10 + (rest[i++] - '0');
+        const std::string part = i < rest.size() ? rest.substr(i) : "";
+        if (i == 5 || e >= s.experts) return set_err(h, NVLLM_ERR_INVALID, "unknown tensor %s", cname);
+        if (part == ".gate") mat(y.moe_in, s.ff, W, W, (size_t)e * 2 * y.ff_p, 2, 0);
+        else if (part == ".up") mat(y.moe_in, s.ff, W, W, (size_t)e * 2 * y.ff_p, 2, 1);
+        else if (part == ".down") mat(y.moe_out, W, s.ff, y.ff_p, (size_t)e * W);
+      }
+    }
   } else if (parse_layer_name(name, &l, &rest) && l < h->L &&
              (h->ll[l].s.mixer == NVLLM_MIXER_GLA || h->ll[l].s.mixer == NVLLM_MIXER_ATTN_TMIX)) {
     // sequential pre-norm blocks: gated linear attention / attention + time mixing, mixture of experts
@@ -279,9 +340,37 @@ int layered_finalize(nvllm_handle* h) {
   std::vector<std::string> need = {"embed", "final.norm"};
   if (h->lm_head_owned) need.push_back("head");
   if (h->loop_step) need.push_back("loop.step");
+  if (h->embed_norm_w) need.push_back("embed.norm");
+  if (h->side_embed) need.push_back("side.embed");
   for (int l = 0; l < h->L; l++) {
     const nvllm_layer_spec& s = h->ll[l].s;
     const std::string p = "l" + std::to_string(l) + ".";
+    if (s.mixer == NVLLM_MIXER_ATTENTION || s.mixer == NVLLM_MIXER_MAMBA2) {
+      need.push_back(p + "norm1");
+      need.push_back(p + "mix.o");
+      if (s.mixer == NVLLM_MIXER_ATTENTION) {
+        for (const char* n : {"mix.q", "mix.k", "mix.v"}) need.push_back(p + n);
+        if (s.qk_norm == 3) { need.push_back(p + "mix.q.norm"); need.push_back(p + "mix.k.norm"); }
+        if (s.v_mix && !h->ll[l].vmix_first) need.push_back(p + "mix.vmix");
+        if (s.sink_learned) need.push_back(p + "mix.sink");
+        if (s.head_temp) need.push_back(p + "mix.temp");
+        if (s.head_gate) need.push_back(p + "mix.g");
+      } else {
+        for (const char* n : {"mix.in", "mix.conv", "mix.conv.b", "mix.dt_bias", "mix.A_log", "mix.D", "mix.norm"})
+          need.push_back(p + n);
+      }
+      if (h->ll[l].canon_w) need.push_back(p + "canon1");
+      if (h->ll[l].side_gate)
+        for (const char* n : {"side.gate", "side.proj", "side.norm"}) need.push_back(p + n);
+      if (s.mlp == NVLLM_MLP_MOE) {
+        need.push_back(p + "norm2");
+        need.push_back(p + "mlp.router");
+        if (s.route_correction) need.push_back(p + "mlp.correction");
+        for (int e = 0; e < s.experts; e++)
+          for (const char* n : {".gate", ".up", ".down"}) need.push_back(p + "mlp.e" + std::to_string(e) + n);
+      }
+      continue;
+    }
     if (s.mixer == NVLLM_MIXER_GLA || s.mixer == NVLLM_MIXER_ATTN_TMIX) {
       need.push_back(p + "norm1");
       if (s.mixer == NVLLM_MIXER_GLA) {
@@ -365,7 +454,7 @@ int layered_finalize(nvllm_handle* h) {
   h->win_vpools.assign(n_pools, nullptr);
   for (size_t r = 0; r < h->runs.size(); r++) {
     const ListedLayer& y = h->ll[h->runs[r].layer];
-    if (y.s.mixer != NVLLM_MIXER_ATTN_TMIX) continue;
+    if (y.s.mixer != NVLLM_MIXER_ATTN_TMIX && y.s.mixer != NVLLM_MIXER_ATTENTION) continue;
     const size_t rows = (size_t)h->num_blocks * y.s.kv_heads * KV_BLOCK;
     const size_t kb = rows * y.s.dim * dt_size(h->kvdt), vb = rows * y.s.vdim * dt_size(h->kvdt);
     cudaError_t e = cudaMalloc(&h->win_kpools[r], kb);
@@ -421,7 +510,17 @@ int layered_finalize(nvllm_handle* h) {
     const int half = r.dims / 2;
     std::vector<double> f(half);
     for (int i = 0; i < half; i++) f[i] = pow(r.base, -2.0 * (double)i / (double)r.dims);
-    if (r.factor > 0) {
+    if (r.factor > 0 && r.piecewise) {
+      for (int i = 0; i < half; i++) {
+        const double wl = 2.0 * M_PI / f[i];
+        if (wl < r.original / r.fast) continue;
+        if (wl > r.original / r.slow) f[i] = f[i] / r.factor;
+        else {
+          const double sm = (r.original / wl - r.slow) / (r.fast - r.slow);
+          f[i] = (1.0 - sm) * f[i] / r.factor + sm * f[i];
+        }
+      }
+    } else if (r.factor > 0) {
       // entry at which a wavelength of original / turns is reached
       auto at = [&](double turns) { return r.dims * log(r.original / (2.0 * M_PI * turns)) / (2.0 * log(r.base)); };
       const double lo = std::max(floor(at(r.fast)), 0.0), hi = std::min(ceil(at(r.slow)), (double)r.dims - 1.0);
@@ -443,12 +542,12 @@ int layered_finalize(nvllm_handle* h) {
 // ------------------------------------------------------------------ sequential post-norm blocks
 // x += w * rmsnorm(pending sublayer result); xn = x in the activation dtype (what the next
 // sublayer reads)
-static int run_postnorm(nvllm_handle* h, Pending* p, const float* w, int T) {
+static int run_postnorm(nvllm_handle* h, Pending* p, const float* w, int T, bool want_y = true) {
   NormArgs a{};
   a.post = 1;
   a.x = h->ws.x;
   a.p1 = p->p; a.S1 = p->S; a.stride1 = p->stride; a.m1 = 1.f;
-  a.w = w; a.eps = h->cfg.norm_eps; a.y = h->ws.xn; a.ydt = h->adt;
+  a.w = w; a.eps = h->cfg.norm_eps; a.y = want_y ? h->ws.xn : nullptr; a.ydt = h->adt;
   a.n_rows = T; a.H = h->H;
   ProfScope ps(h, NVLLM_K_NORM, (double)T * h->H * (4 * 3 + dt_size(h->adt)), 0, (double)T * h->H * 4 * (p->S - 1));
   LAUNCH(h, launch_norm(h->stream, a));
@@ -593,11 +692,15 @@ static LinSeg seg_of(const Pending& p, int ld, int col) {
 
 // x += pending sublayer results (+ the vector that opens a pass); xn = RMSNorm(x) * w.  With `moe`
 // the kernel also routes the normed row and computes the always-on expert's gate.
+// f32_out: the normed row goes out in fp32 (to xn_f32) instead of the activation dtype — the input of the
+// convolution that precedes a mixer.  plain: no norm, xn = the updated x itself.
 static int run_prenorm(nvllm_handle* h, Pending* p1, Pending* p2, const float* row_m2, const float* xadd, const float* w,
-                       const ListedLayer* moe, int T) {
+                       const ListedLayer* moe, int T, bool f32_out = false, bool plain = false) {
   Workspace& ws = h->ws;
   NormArgs a{};
   a.x = ws.x;
+  a.groups = h->norm_groups;
+  a.plain = plain ? 1 : 0;
   double bytes = (double)T * h->H * (4 + dt_size(h->adt)), impl = 0.0;
   if (p1->p) {
     a.p1 = p1->p; a.S1 = p1->S; a.stride1 = p1->stride; a.m1 = p1->m; a.bias1 = p1->bias;
@@ -613,12 +716,14 @@ static int run_prenorm(nvllm_handle* h, Pending* p1, Pending* p2, const float* r
   }
   a.xadd = xadd;
   a.w = w; a.eps = h->cfg.norm_eps; a.y = ws.xn; a.ydt = h->adt;
+  if (f32_out) { a.y = nullptr; a.y_f32 = ws.xn_f32; }
   a.n_rows = T; a.H = h->H;
   if (moe) {
     const nvllm_layer_spec& s = moe->s;
     a.router = moe->router; a.E = s.experts; a.topk = s.top;
     a.topk_idx = ws.topk_idx; a.topk_w = ws.topk_w;
-    a.route = RouteOpts{0, 0, 1, 1.f, s.route_sigmoid, s.weight_on_input};
+    a.route = RouteOpts{s.groups, s.keep_groups, s.route_norm ? 0 : 1, 1.f, s.route_sigmoid, s.weight_on_input,
+                        s.route_correction ? moe->route_corr : nullptr, s.group_top2};
     if (s.shared_ff > 0) { a.gate_w = moe->sh_gate; a.gate_out = ws.sh_gate; }
     bytes += (double)s.experts * h->H * 4;
   }
@@ -821,6 +926,134 @@ static int ffn_moe_relu2(nvllm_handle* h, const ListedLayer& y, Pending* p1, Pen
   return run_gemm(h, w.hbuf, ff, y.w2, T, H, ff, 1.f, w.ws_b, w.ws_b_floats, H, p2);
 }
 
+// Grouped-query attention over the whole cached prefix with the options of the spec (attention_window.cu)
+static int mixer_attention(nvllm_handle* h, const ListedLayer& y, int run_idx, Pending* out) {
+  const StepLayout& L = h->lay;
+  Workspace& w = h->ws;
+  const nvllm_layer_spec& s = y.s;
+  const int T = L.T, H = h->H;
+  const int32_t* d = L.d;
+  const double asz = dt_size(h->adt), kvsz = dt_size(h->kvdt);
+  int rc;
+  Pending pin;
+  if ((rc = run_gemm(h, w.xn, H, y.w_in, T, y.n_in, H, 1.f, w.ws_a, w.ws_a_floats, y.n_in, &pin))) return rc;
+  WinAttnArgs a{};
+  a.T = T; a.n_seqs = L.n; a.H = s.heads; a.G = s.kv_heads; a.dim = s.dim; a.vdim = s.vdim;
+  a.softcap = s.softcap; a.sink = s.sink; a.qk_norm = s.qk_norm; a.own_kv = 1;
+  a.eps = h->cfg.norm_eps; a.scale = s.scale;
+  a.in_p = pin.p; a.in_S = pin.S; a.in_stride = pin.stride; a.in_ld = y.n_in;
+  a.slots = d + L.slots;
+  a.kpool = h->win_kpools[run_idx]; a.vpool = h->win_vpools[run_idx];
+  a.q = w.q; a.out = w.attn_out; a.o_ld = y.ov_p;
+  a.block_tables = d + L.block_tables; a.max_blocks = L.max_blocks;
+  a.cu_q = d + L.cu_q; a.seq_start = d + L.seq_start; a.seq_len = d + L.seq_len;
+  a.qnorm_w = y.qnorm_w; a.knorm_w = y.knorm_w;
+  if (y.rope >= 0) {
+    const RopeTable& rt = h->ropes[y.rope];
+    a.rot_half = s.rot_dims / 2; a.rot_pairs = s.rot_pairs; a.cosT = rt.cosT; a.sinT = rt.sinT;
+  }
+  a.positions = d + L.positions;
+  a.qtemp_coef = s.qtemp_coef; a.qtemp_every = s.qtemp_every;
+  a.head_scale = s.head_temp ? y.head_temp : nullptr;
+  if (s.v_mix) {
+    a.vfirst = w.v_first; a.vfirst_write = y.vmix_first;
+    a.vmix = y.vmix_first ? nullptr : y.vmix;
+  }
+  if (s.head_gate) { a.gate_out = w.att_gate; a.gate = w.att_gate; a.gate_ld = s.heads; a.gate_head = 1; }
+  a.slope_exp = s.dist_slope;
+  a.sink_w = s.sink_learned ? y.sink_w : nullptr;
+  if (L.prefill) {
+    a.tile_seq = d + L.tile_seq; a.tile_q0 = d + L.tile_q0; a.n_tiles = L.n_qtiles; a.qtile = h->attn_qtile;
+  } else {
+    a.n_tiles = L.n; a.qtile = 1;
+  }
+  {
+    ProfScope ps(h, NVLLM_K_ROPE_KV,
+                 (double)T * y.n_in * 4 + (double)T * (y.n_q * asz + (y.n_k + y.n_v) * kvsz), 0,
+                 (double)T * y.n_in * 4 * (pin.S - 1));
+    LAUNCH(h, launch_winattn_prep(h->stream, h->adt, h->kvdt, a));
+  }
+  {
+    // algorithmic: the K / V rows of every context once per step; flops over the visible pairs
+    ProfScope ps(h, L.prefill ? NVLLM_K_ATTN_PREFILL : NVLLM_K_ATTN_DECODE,
+                 (double)L.sum_len * s.kv_heads * (s.dim + s.vdim) * kvsz, 2.0 * s.heads * (s.dim + s.vdim) * L.attn_pairs,
+                 (double)T * (s.heads * s.dim + y.ov_p) * asz);
+    LAUNCH(h, launch_winattn(h->stream, h->adt, h->kvdt, a));
+  }
+  return run_gemm(h, w.attn_out, y.ov_p, y.w_o, T, H, y.ov_p, 1.f, w.ws_b, w.ws_b_floats, H, out);
+}
+
+// Mamba-2 between its two projections: convolution / step sizes / decays (mamba.cu), the scan of
+// linrec.cu (k = B, q = C of the head's group, v = dt x, one decay per token and head), D skip + gate +
+// grouped norm (mamba.cu).  *pin_out: the input projection's partials (the convolution's inputs, for the tail).
+static int mixer_mamba2(nvllm_handle* h, const ListedLayer& y, const LayerRun& r, Pending* pin_out, Pending* out) {
+  const StepLayout& L = h->lay;
+  Workspace& w = h->ws;
+  const nvllm_layer_spec& s = y.s;
+  const int T = L.T, H = h->H;
+  const int32_t* d = L.d;
+  const double asz = dt_size(h->adt);
+  const int inner = s.heads * s.vdim, gn = s.ssm_groups * s.state, ch = y.conv_ch;
+  int rc;
+  Pending pin;
+  if ((rc = run_gemm(h, w.xn, H, y.w_in, T, y.n_in, H, 1.f, w.ws_a, w.ws_a_floats, y.n_in, &pin))) return rc;
+  *pin_out = pin;
+  Mamba2SlotArgs m{};
+  m.T = T; m.n_seqs = L.n; m.heads = s.heads; m.vdim = s.vdim; m.N = s.state; m.G = s.ssm_groups; m.taps = s.conv;
+  m.norm_groups = s.norm_groups; m.eps = h->cfg.norm_eps; m.fast_act = h->adt == DT_BF16;
+  m.in_p = pin.p; m.in_S = pin.S; m.in_stride = pin.stride; m.in_ld = y.n_in;
+  m.conv_w = y.conv_w; m.conv_b = y.conv_b; m.dt_bias = y.dt_bias; m.a_log = y.a_log; m.d_skip = y.d_skip; m.norm_w = y.onorm_w;
+  m.cu_q = d + L.cu_q; m.positions = d + L.positions; m.state_slots = d + L.state_slots;
+  m.state_pool = h->state_pool; m.slot_floats = h->state_slot_floats; m.tail_off = r.tail_off;
+  m.xbc = w.m2_xbc; m.dtx = w.m2_dtx; m.decay = w.m2_decay; m.o = w.lr_o;
+  m.out = w.attn_out; m.o_ld = y.ov_p;
+  {
+    ProfScope ps(h, NVLLM_K_RECUR, (double)T * ((ch + s.heads) * 4 + (ch + inner + s.heads) * 4), 0,
+                 (double)T * y.n_in * 4 * (pin.S - 1) + (double)T * ch * 4 * (s.conv - 1));
+    LAUNCH(h, launch_mamba2_slot_prep(h->stream, m));
+  }
+  LinRecArgs b{};
+  linrec_common(h, &b, r);
+  b.H = s.heads; b.dim = s.state; b.vdim = s.vdim; b.tmix = 0; b.tau = 1.f; b.qmul = 1.f;
+  b.q = LinSeg{w.m2_xbc + inner + gn, 1, 0, ch};
+  b.k = LinSeg{w.m2_xbc + inner, 1, 0, ch};
+  b.v = LinSeg{w.m2_dtx, 1, 0, inner};
+  b.qk_div = s.heads / s.ssm_groups;
+  b.decay_p = w.m2_decay; b.decay_ld = s.heads;
+  {
+    // algorithmic: every sequence's state once in and once out, the token inputs once, the read-outs once
+    const double state = (double)L.n * inner * s.state * 4 * 2;
+    ProfScope ps(h, NVLLM_K_RECUR, state + (double)T * (2.0 * gn + 2.0 * inner + s.heads) * 4, 4.0 * T * inner * s.state);
+    LAUNCH(h, launch_linrec_scan(h->stream, b));
+  }
+  {
+    ProfScope ps(h, NVLLM_K_RECUR, (double)T * inner * (4 + 4 + 4 + asz), 0, (double)T * inner * 4 * (pin.S - 1));
+    LAUNCH(h, launch_mamba2_slot_out(h->stream, h->adt, m));
+  }
+  return run_gemm(h, w.attn_out, y.ov_p, y.w_o, T, H, y.ov_p, 1.f, w.ws_b, w.ws_b_floats, H, out);
+}
+
+// Per-layer token input after the feed-forward: x += rmsnorm(W_proj (gelu_tanh(W_gate x) * e)) * w, e = the
+// token's entries of this layer's part of the side table.  The pending results join x first (the
+// gate reads the updated stream itself, not a normed copy).
+static int token_side_input(nvllm_handle* h, const ListedLayer& y, int layer, Pending* p1, Pending* p2, const float* row_m2) {
+  const StepLayout& L = h->lay;
+  Workspace& w = h->ws;
+  const int T = L.T, H = h->H, sp = h->side_p;
+  int rc;
+  if ((rc = run_prenorm(h, p1, p2, row_m2, nullptr, nullptr, nullptr, T, false, true))) return rc;
+  Pending pg;
+  if ((rc = run_gemm(h, w.xn, H, y.side_gate, T, sp, H, 1.f, w.ws_a, w.ws_a_floats, sp, &pg))) return rc;
+  {
+    ProfScope ps(h, NVLLM_K_ACT, (double)T * sp * (4 + dt_size(h->wdt) + dt_size(h->adt)), 0, (double)T * sp * 4 * (pg.S - 1));
+    LAUNCH(h, launch_token_gate(h->stream, h->adt, h->wdt, T, h->side_dim, pg.p, pg.S, pg.stride, sp, L.d + L.tokens,
+                                h->side_embed, h->L * h->side_dim, layer * h->side_dim, w.side_g, sp));
+  }
+  Pending pp;
+  if ((rc = run_gemm(h, w.side_g, sp, y.side_proj, T, H, sp, 1.f, w.ws_b, w.ws_b_floats, H, &pp))) return rc;
+  return run_postnorm(h, &pp, y.side_norm, T, false);
+}
+
 // *row_m2_out: per-row multiplier of the second addend still pending at the end (or null)
 static int forward_layers_prenorm(nvllm_handle* h, Pending* p1, Pending* p2, const float** row_m2_out) {
   const int T = h->lay.T;
@@ -830,19 +1063,62 @@ static int forward_layers_prenorm(nvllm_handle* h, Pending* p1, Pending* p2, con
     const LayerRun& r = h->runs[ri];
     const ListedLayer& y = h->ll[r.layer];
     const float* xadd = r.pass_start >= 0 ? h->loop_step + (size_t)r.pass_start * h->H : nullptr;
-    if ((rc = run_prenorm(h, p1, p2, row_m2, xadd, y.post1_w, nullptr, T))) return rc;
+    const bool conv_in = y.canon_w != nullptr;  // the mixer reads h + conv(h)
+    if ((rc = run_prenorm(h, p1, p2, row_m2, xadd, y.post1_w, nullptr, T, conv_in))) return rc;
     row_m2 = nullptr;
-    Pending pa, pb;
+    const StepLayout& L = h->lay;
+    const int32_t* d = L.d;
+    if (conv_in) {
+      ProfScope ps(h, NVLLM_K_RECUR, (double)T * h->H * (4 + dt_size(h->adt)), 2.0 * T * h->H * h->mixer_conv,
+                   (double)T * h->H * 4 * (h->mixer_conv - 1));
+      LAUNCH(h, launch_mixer_conv(h->stream, h->adt, T, L.n, h->H, h->mixer_conv, h->ws.xn_f32, y.canon_w, d + L.cu_q,
+                                  d + L.positions, d + L.state_slots, h->state_pool, h->state_slot_floats, r.canon_off,
+                                  h->ws.xn));
+    }
+    Pending pa, pb, pin;
     if (y.s.mixer == NVLLM_MIXER_GLA) rc = mixer_gla(h, y, r, &pa);
+    else if (y.s.mixer == NVLLM_MIXER_ATTENTION) rc = mixer_attention(h, y, (int)ri, &pa);
+    else if (y.s.mixer == NVLLM_MIXER_MAMBA2) rc = mixer_mamba2(h, y, r, &pin, &pa);
     else rc = mixer_attn_tmix(h, y, r, (int)ri, &pa, &pb);
     if (rc) return rc;
-    if (y.s.mlp == NVLLM_MLP_MOE) {
+    if (conv_in || y.s.mixer == NVLLM_MIXER_MAMBA2) {
+      // the slot's tails move on: the normed rows the mixer's convolution read (still in xn_f32) and Mamba-2's
+      // convolution inputs (still in ws_a: the output projection wrote elsewhere)
+      TailJob jobs[2];
+      int nj = 0;
+      double bytes = 0;
+      if (conv_in) {
+        TailJob& j = jobs[nj++];
+        j.seg = LinSeg{h->ws.xn_f32, 1, 0, h->H}; j.bias = nullptr; j.act = nullptr;
+        j.channels = h->H; j.taps = h->mixer_conv; j.tail_off = r.canon_off;
+        bytes += (double)L.n * (h->mixer_conv - 1) * h->H * 8;
+      }
+      if (y.s.mixer == NVLLM_MIXER_MAMBA2 && y.s.conv > 1) {
+        TailJob& j = jobs[nj++];
+        j.seg = seg_of(pin, y.n_in, y.s.heads * y.s.vdim); j.bias = nullptr; j.act = nullptr;
+        j.channels = y.conv_ch; j.taps = y.s.conv; j.tail_off = r.tail_off;
+        bytes += (double)L.n * (y.s.conv - 1) * y.conv_ch * 8;
+      }
+      if (nj) {
+        ProfScope ps(h, NVLLM_K_RECUR, bytes, 0);
+        LAUNCH(h, launch_roll_tails(h->stream, h->adt, L.n, jobs, nj, d + L.cu_q, d + L.positions, d + L.state_slots,
+                                    h->state_pool, h->state_slot_floats));
+      }
+    }
+    if (y.s.mlp == NVLLM_MLP_MOE && y.s.act == NVLLM_FFN_SWIGLU) {
+      if ((rc = run_prenorm(h, &pa, &pb, nullptr, nullptr, y.post2_w, &y, T))) return rc;
+      if ((rc = run_moe_ffn(h, T, h->ws.xn, y.s.experts, y.s.top, y.ff_p, 0.f, y.moe_in, y.moe_out, h->ws.topk_w, p1))) return rc;
+    } else if (y.s.mlp == NVLLM_MLP_MOE) {
       if ((rc = run_prenorm(h, &pa, &pb, nullptr, nullptr, y.post2_w, &y, T))) return rc;
       if ((rc = ffn_moe_relu2(h, y, p1, p2))) return rc;
       row_m2 = p2->p ? h->ws.sh_gate : nullptr;
     } else {
       *p1 = pa;
       *p2 = pb;
+    }
+    if (y.side_gate) {
+      if ((rc = token_side_input(h, y, r.layer, p1, p2, row_m2))) return rc;
+      row_m2 = nullptr;
     }
   }
   h->glu_limit_cur = 0.f;
@@ -865,6 +1141,13 @@ int forward_step_layered(nvllm_handle* h) {
     const bool seq_style = h->block_style == NVLLM_LBLOCK_SEQUENTIAL_POSTNORM;
     LAUNCH(h, launch_embed(st, h->wdt, d + L.tokens, d_pos, h->wte, nullptr, 0, h->cfg.embedding_multiplier,
                            w.x, T, H, nullptr, nullptr, nullptr, h->pos_freq, seq_style ? w.xn : nullptr));
+  }
+  if (h->embed_norm_w) {  // the embedding is normed in place: x <- norm(x) * w
+    NormArgs a{};
+    a.x = w.x; a.w = h->embed_norm_w; a.eps = h->cfg.norm_eps; a.y = nullptr; a.ydt = h->adt; a.y_f32 = w.x;
+    a.n_rows = T; a.H = H; a.groups = h->norm_groups;
+    ProfScope ps(h, NVLLM_K_NORM, (double)T * H * 8, 0);
+    LAUNCH(h, launch_norm(st, a));
   }
   for (auto& r : h->ropes) {
     ProfScope ps(h, NVLLM_K_MISC, (double)T * r.dims * 4, 0);
@@ -989,7 +1272,8 @@ int forward_step_layered(nvllm_handle* h) {
                      h->block_style == NVLLM_LBLOCK_PARALLEL_PRENORM, row_m2)))
     return rc;
   Pending lg;
-  if ((rc = run_gemm(h, w.xn_last, H, h->lm_head, n_out, h->V, H, 1.f, w.logits_p, w.logits_p_floats, h->ldl, &lg, 0,
+  if ((rc = run_gemm(h, w.xn_last, H, h->lm_head, n_out, h->V, H, h->logit_scale != 0.f ? h->logit_scale : 1.f, w.logits_p,
+                     w.logits_p_floats, h->ldl, &lg, 0,
                      nullptr, 0, nullptr, nullptr, 0, (double)n_out * h->V * 4)))
     return rc;
   {
@@ -1029,9 +1313,49 @@ extern "C" int nvllm_create_layered(const nvllm_layered_config* c, const nvllm_l
   const bool has_loop = c->loop_times >= 1 && c->loop_stop > c->loop_start;
   if (has_loop && (!pre_style || c->loop_start < 0 || c->loop_stop > c->num_layers))
     return bad(-1, "a repeated run of layers needs the sequential pre-norm block style and 0 <= start < stop <= layers");
+  if ((c->norm_groups > 1 || c->embed_norm || c->mixer_conv > 1 || c->side_dim > 0) && !pre_style)
+    return bad(-1, "grouped norms, a normed embedding, the convolution on the mixers' input and the per-layer token input need the sequential pre-norm block style");
+  if (c->norm_groups > 64 || (c->norm_groups > 1 && c->hidden % c->norm_groups)) return bad(-1, "norm groups must divide the width (at most 64)");
+  if (c->mixer_conv < 0 || c->mixer_conv > 8) return bad(-1, "convolution on the mixers' input: at most 8 taps");
+  if (c->side_dim < 0) return bad(-1, "negative side_dim");
+  int vmix_first = -1;
   for (int l = 0; l < c->num_layers; l++) {
     const nvllm_layer_spec& s = layers[l];
     const bool seq_style = c->block_style == NVLLM_LBLOCK_SEQUENTIAL_POSTNORM;
+    if (s.mixer == NVLLM_MIXER_ATTENTION || s.mixer == NVLLM_MIXER_MAMBA2) {
+      if (!pre_style) return bad(l, "attention with options / Mamba-2 need the sequential pre-norm block style");
+      if (s.heads <= 0 || s.vdim <= 0) return bad(l, "non-positive mixer size");
+      if (s.mixer == NVLLM_MIXER_ATTENTION) {
+        if (s.kv_heads <= 0 || s.dim <= 0 || s.heads % s.kv_heads) return bad(l, "heads must be a multiple of kv_heads");
+        if (s.vdim > 512 || s.dim > 1024) return bad(l, "attention: dim <= 1024, vdim <= 512");
+        if (s.qk_norm != 0 && s.qk_norm != 1 && s.qk_norm != 3) return bad(l, "attention: qk_norm 0, 1 (per head) or 3 (per head, weighted)");
+        if (s.rot_dims < 0 || s.rot_dims > s.dim || (s.rot_dims & 1)) return bad(l, "rotated entries must be even and <= dim");
+        if (s.rot_piecewise && !(s.rot_factor > 0.f && s.rot_fast != s.rot_slow)) return bad(l, "piecewise frequency scaling: factor > 0, two different bounds");
+        if (s.qtemp_coef > 0.f && s.qtemp_every <= 0) return bad(l, "query temperature: a positive step");
+        if (s.sink_learned && !s.sink) return bad(l, "a learned sink needs sink = 1");
+        if (s.v_mix) {
+          if (vmix_first < 0) vmix_first = l;
+          else if (layers[vmix_first].kv_heads != s.kv_heads || layers[vmix_first].vdim != s.vdim)
+            return bad(l, "layers that mix values must have the first such layer's kv_heads and vdim");
+        }
+      } else {
+        if (s.state <= 0 || s.state > LINREC_MAX_DIM) return bad(l, "Mamba-2: 0 < state <= 256");
+        if (s.ssm_groups <= 0 || s.heads % s.ssm_groups) return bad(l, "Mamba-2: heads must be a multiple of the groups");
+        if (s.heads > 256) return bad(l, "Mamba-2: at most 256 heads");
+        if (s.norm_groups <= 0 || s.norm_groups > 64 || (s.heads * s.vdim) % s.norm_groups) return bad(l, "Mamba-2: norm groups must divide heads * vdim (at most 64)");
+        if (s.conv < 1 || s.conv > 8) return bad(l, "convolution taps 1..8");
+      }
+      if (s.mlp != NVLLM_MLP_NONE && s.mlp != NVLLM_MLP_MOE) return bad(l, "pre-norm blocks: feed-forward none or mixture of experts");
+      if (s.mlp == NVLLM_MLP_MOE) {
+        if (s.act != NVLLM_FFN_SWIGLU) return bad(l, "these blocks take gated experts W_down (silu(W_gate h) * W_up h)");
+        if (s.ff <= 0 || s.experts <= 0 || s.experts > 256 || s.top <= 0 || s.top > 32 || s.top > s.experts)
+          return bad(l, "ff > 0, experts 1..256, top 1..32");
+        const int g = s.groups > 0 ? s.groups : 1, keep = s.groups > 0 ? s.keep_groups : 1;
+        if (s.experts % g || keep <= 0 || keep > g || keep * (s.experts / g) < s.top)
+          return bad(l, "expert groups must divide the experts and the kept groups must hold `top` experts");
+      }
+      continue;
+    }
     if (s.mixer == NVLLM_MIXER_GLA || s.mixer == NVLLM_MIXER_ATTN_TMIX) {
       if (!pre_style) return bad(l, "gated linear attention / attention + time mixing need the sequential pre-norm block style");
       if (s.heads <= 0 || s.dim <= 0 || s.vdim <= 0 || s.lowrank <= 0) return bad(l, "non-positive mixer size");
@@ -1146,6 +1470,11 @@ extern "C" int nvllm_create_layered(const nvllm_layered_config* c, const nvllm_l
   h->block_style = c->block_style;
   h->position_kind = c->position;
   h->norm_offset = c->norm_offset;
+  h->norm_groups = c->norm_groups > 1 ? c->norm_groups : 0;
+  h->mixer_conv = c->mixer_conv > 1 ? c->mixer_conv : 0;
+  h->side_dim = c->side_dim;
+  h->side_p = (int)up8((size_t)c->side_dim);
+  h->logit_scale = c->logit_scale;
   if (pre_style) {
     g.num_kv_heads = layers[0].kv_heads > 0 ? layers[0].kv_heads : layers[0].heads; g.head_dim = layers[0].dim;
     g.attention_type = NVLLM_ATTN_GQA; g.norm_type = NVLLM_NORM_RMS; g.position_type = NVLLM_POS_ROPE;
@@ -1186,12 +1515,90 @@ extern "C" int nvllm_create_layered(const nvllm_layered_config* c, const nvllm_l
     h->lm_head_owned = true;
   }
   AL(h->lnf_w, (size_t)W * 4);
+  if (c->embed_norm) AL(h->embed_norm_w, (size_t)W * 4);
+  if (h->side_dim > 0) AL(h->side_embed, (size_t)h->V * h->L * h->side_dim * wsz);
   h->ll.resize(h->L);
   int qkv_cols = 0, q_cols = 0, win_qtile = 0;
   for (int l = 0; l < h->L; l++) {
     ListedLayer& y = h->ll[l];
     y.s = layers[l];
     const nvllm_layer_spec& s = y.s;
+    if (pre_style && h->mixer_conv) AL(y.canon_w, (size_t)W * h->mixer_conv * 4);
+    if (pre_style && h->side_dim > 0) {
+      AL(y.side_gate, (size_t)h->side_p * W * wsz);
+      AL(y.side_proj, (size_t)W * h->side_p * wsz);
+      AL(y.side_norm, (size_t)W * 4);
+      qkv_cols = std::max(qkv_cols, h->side_p);
+    }
+    if (s.mixer == NVLLM_MIXER_ATTENTION || s.mixer == NVLLM_MIXER_MAMBA2) {
+      const int hv = s.heads * s.vdim;
+      y.ov_p = (int)up8((size_t)hv);
+      y.ff_p = (int)up8((size_t)std::max(s.ff, 0));
+      AL(y.post1_w, (size_t)W * 4);
+      if (s.mixer == NVLLM_MIXER_ATTENTION) {
+        y.n_q = s.heads * s.dim; y.n_k = s.kv_heads * s.dim; y.n_v = s.kv_heads * s.vdim;
+        y.n_in = y.n_q + y.n_k + y.n_v + (s.head_gate ? s.heads : 0);  // Q | K | V | head gates
+        AL(y.w_in, (size_t)y.n_in * W * wsz);
+        if (s.qk_norm == 3) {
+          AL(y.qnorm_w, (size_t)s.dim * 4);
+          AL(y.knorm_w, (size_t)s.dim * 4);
+        }
+        if (s.v_mix) {
+          AL(y.vmix, 4);
+          y.vmix_first = l == vmix_first;
+        }
+        if (s.sink_learned) AL(y.sink_w, (size_t)s.heads * 4);
+        if (s.head_temp) AL(y.head_temp, (size_t)s.heads * 4);
+        if (s.rot_dims > 0) {
+          for (size_t r = 0; r < h->ropes.size(); r++) {
+            const RopeTable& t = h->ropes[r];
+            if (t.base == (double)s.rot_base && t.dims == s.rot_dims && t.factor == (double)s.rot_factor &&
+                t.original == (double)s.rot_original && t.fast == (double)s.rot_fast && t.slow == (double)s.rot_slow &&
+                t.piecewise == (s.rot_piecewise != 0))
+              y.rope = (int)r;
+          }
+          if (y.rope < 0) {
+            RopeTable rt;
+            rt.base = s.rot_base; rt.dims = s.rot_dims;
+            rt.factor = s.rot_factor; rt.original = s.rot_original; rt.fast = s.rot_fast; rt.slow = s.rot_slow;
+            rt.piecewise = s.rot_piecewise != 0;
+            y.rope = (int)h->ropes.size();
+            h->ropes.push_back(rt);
+          }
+        }
+        const int qt = winattn_qtile(h->adt, h->kvdt, s.dim, s.vdim);
+        win_qtile = win_qtile ? std::min(win_qtile, qt) : qt;
+        q_cols = std::max(q_cols, std::max(y.n_q, y.ov_p));
+      } else {
+        const int gn = s.ssm_groups * s.state;
+        y.conv_ch = hv + 2 * gn;
+        y.n_in = 2 * hv + 2 * gn + s.heads;  // z | x | B | C | dt
+        AL(y.w_in, (size_t)y.n_in * W * wsz);
+        AL(y.conv_w, (size_t)y.conv_ch * s.conv * 4);
+        AL(y.conv_b, (size_t)y.conv_ch * 4);
+        AL(y.dt_bias, (size_t)s.heads * 4);
+        AL(y.a_log, (size_t)s.heads * 4);
+        AL(y.d_skip, (size_t)s.heads * 4);
+        AL(y.onorm_w, (size_t)hv * 4);
+        q_cols = std::max(q_cols, y.ov_p);
+      }
+      AL(y.w_o, (size_t)W * y.ov_p * wsz);
+      if (s.mlp == NVLLM_MLP_MOE) {
+        AL(y.post2_w, (size_t)W * 4);
+        AL(y.router, (size_t)s.experts * W * 4);
+        if (s.route_correction) AL(y.route_corr, (size_t)s.experts * 4);
+        AL(y.moe_in, (size_t)s.experts * 2 * y.ff_p * W * wsz);
+        AL(y.moe_out, (size_t)s.experts * W * y.ff_p * wsz);
+        h->moe = true;
+        h->E = std::max(h->E, s.experts);
+        h->topk = std::max(h->topk, s.top);
+        h->F = std::max(h->F, y.ff_p);
+      }
+      qkv_cols = std::max(qkv_cols, y.n_in);
+      h->nh = std::max(h->nh, s.heads);
+      h->hd = std::max(h->hd, s.vdim);
+      continue;
+    }
     if (s.mixer == NVLLM_MIXER_GLA || s.mixer == NVLLM_MIXER_ATTN_TMIX) {
       const int hd = s.heads * s.dim, hv = s.heads * s.vdim;
       y.ov_p = (int)up8((size_t)hv);
@@ -1373,7 +1780,17 @@ extern "C" int nvllm_create_layered(const nvllm_layered_config* c, const nvllm_l
       // every piece starts on a 16-byte boundary (the kernels read them with 16-byte loads)
       auto up4 = [](size_t n) { return (n + 3) / 4 * 4; };
       r.state_off = up4(h->state_slot_floats);
-      if (s.mixer == NVLLM_MIXER_GLA) {
+      if (h->mixer_conv) {  // tail of the convolution on the mixer's input, every layer
+        r.canon_off = r.state_off;
+        h->state_slot_floats = up4(r.canon_off + (size_t)(h->mixer_conv - 1) * W);
+        r.state_off = h->state_slot_floats;
+      }
+      if (s.mixer == NVLLM_MIXER_ATTENTION) {
+        // no state of its own
+      } else if (s.mixer == NVLLM_MIXER_MAMBA2) {
+        r.tail_off = up4(r.state_off + (size_t)s.heads * s.state * s.vdim);
+        h->state_slot_floats = up4(r.tail_off + (size_t)(s.conv - 1) * h->ll[l].conv_ch);
+      } else if (s.mixer == NVLLM_MIXER_GLA) {
         h->state_slot_floats = up4(r.state_off + (size_t)s.heads * s.dim * s.vdim);
       } else {
         r.tail_off = up4(r.state_off + (size_t)s.heads2 * s.dim2 * s.dim2);

@@ -243,6 +243,7 @@ static int run_norm(nvllm_handle* h, float* x, Pending* p1, Pending* p2, const f
   a.w = w; a.b = b; a.eps = h->cfg.norm_eps; a.y = y; a.ydt = h->adt; a.y_f32 = y_f32;
   a.row_idx = row_idx; a.n_rows = n_rows; a.H = h->H;
   a.row_bias = row_idx ? h->view_r0 : 0;  // row_idx holds rows of the whole step
+  a.groups = h->norm_groups;  // > 1: RMS norm in equal parts of the row (layered pre-norm models)
   ProfScope ps(h, NVLLM_K_NORM, bytes, 0, impl);
   LAUNCH(h, launch_norm(h->stream, a));
   if (p1) *p1 = Pending();

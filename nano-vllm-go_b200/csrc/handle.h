@@ -82,6 +82,18 @@ struct ListedLayer {
   // always-on expert in w1 [sff_p, W] / w2 [W, sff_p] with its gate row sh_gate [W] fp32
   float* sh_gate = nullptr;
   int sff_p = 0;
+  // ---- attention with options (NVLLM_MIXER_ATTENTION): fused projection rows [Q | K | V | head gates] in w_in,
+  // per-head norm weights [dim] in qnorm_w / knorm_w, W_o in w_o
+  float *sink_w = nullptr, *head_temp = nullptr, *vmix = nullptr;  // [heads], [heads], [1]
+  int vmix_first = 0;               // this layer's values are the ones later layers mix in
+  // ---- Mamba-2 (NVLLM_MIXER_MAMBA2): input projection rows [z | x | B | C | dt] in w_in, convolution taps
+  // [conv_ch, taps] in conv_w with bias conv_b, a_log / dt_bias / d_skip [heads], norm weight [inner] in onorm_w
+  float *conv_b = nullptr, *d_skip = nullptr;
+  // ---- options of the sequential pre-norm blocks
+  float* route_corr = nullptr;      // [experts]: added to the scores for the choice of experts only
+  float* canon_w = nullptr;         // [W, taps]: convolution on what the mixer reads
+  void *side_gate = nullptr, *side_proj = nullptr;  // per-layer token input: [side_p, W], [W, side_p]
+  float* side_norm = nullptr;       // [W]
 };
 // One execution of a layer: a layer inside a repeated run of layers executes once per pass, every
 // time with caches and state of its own.
@@ -91,6 +103,7 @@ struct LayerRun {
   size_t state_off = 0;  // recurrent state [heads][dim][vdim] (time mixing: [heads2][dim2][dim2]) inside a slot
   size_t tail_off = 0;   // attention side: convolution tail [taps - 1][n_q + n_k + n_v]
   size_t shift_off = 0;  // time mixing: the previous token's input [W]
+  size_t canon_off = 0;  // tail [taps - 1][W] of the convolution on the mixer's input
 };
 struct RopeTable {
   double base = 0;
@@ -99,6 +112,9 @@ struct RopeTable {
   // interpolated frequencies (factor > 0): entry i keeps f_i where its wavelength is short, takes
   // f_i / factor where it is long, a linear ramp between; mult multiplies cos and sin
   double factor = 0, original = 0, fast = 0, slow = 0, mult = 1.0;
+  // piecewise: by wavelength l = 2 pi / f — f kept where l < original / fast, f / factor where
+  // l > original / slow, the blend (1 - s) f / factor + s f between (s = (original / l - slow) / (fast - slow)); mult stays 1
+  bool piecewise = false;
   float *cosT = nullptr, *sinT = nullptr;  // [T_cap, dims / 2] of the current step's rows
 };
 
@@ -167,6 +183,11 @@ struct Workspace {
   // the always-on expert's gate [T] fp32
   float *lr_qkw = nullptr, *lr_v = nullptr, *lr_o = nullptr, *att_gate = nullptr, *sh_gate = nullptr;
   void* mx_in = nullptr;
+  // Mamba-2 with state slots: activated convolution outputs [T, max channels], dt x [T, max inner], decays [T, max heads];
+  // the values of the first value-mixing attention layer [T, kv_heads vdim] fp32; the per-layer token input's gated
+  // vector [T, side_p] act dtype
+  float *m2_xbc = nullptr, *m2_dtx = nullptr, *m2_decay = nullptr, *v_first = nullptr;
+  void* side_g = nullptr;
   float* moe_Y = nullptr;  // [T k, H]
   float* moe_y = nullptr;  // [T, H]
   void* moe_xs = nullptr;  // [T k, H] bf16: normed activations in expert-sorted order
@@ -234,6 +255,11 @@ struct nvllm_handle {
   std::vector<nvllm::LayerRun> runs;
   float* loop_step = nullptr;
   int loop_start = 0, loop_stop = 0, loop_times = 0;  // times >= 1 with stop > start: a repeated run exists
+  // further options of the sequential pre-norm blocks (nvllm_layered_config)
+  int norm_groups = 0, mixer_conv = 0, side_dim = 0, side_p = 0;
+  float* embed_norm_w = nullptr;   // [W] or null
+  void* side_embed = nullptr;      // [V, L * side_dim] weight dtype
+  float logit_scale = 0.f;
   int block_style = 0, position_kind = 0;
   float norm_offset = 0.f;               // added to every norm weight at load
   double* pos_freq = nullptr;            // sinusoidal positions: 10000^(-2i / W), i < W / 2, on the device

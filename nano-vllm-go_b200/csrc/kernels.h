@@ -42,10 +42,15 @@ cudaError_t launch_embed(cudaStream_t st, int wdt, const int* tokens, const int*
 // sigmoid != 0: an expert's score is sigmoid(logit) on its own (no softmax over the experts).
 // square != 0: the weight written is the square of that (a weight w on the INPUT of an expert
 // W_down relu(W_up .)^2 equals w^2 on its output, for w > 0).
+// correction != null: the CHOICE (groups and experts) goes by score + correction[e]; the weights
+// still come from the scores themselves.  group_top2 != 0: a group scores as the sum of its two
+// best choice scores.  With raw == 0 the chosen scores are divided by their sum (+ 1e-20 with sigmoid scores).
 struct RouteOpts {
   int groups, keep, raw;
   float scale;
   int sigmoid, square;
+  const float* correction;
+  int group_top2;
 };
 struct NormArgs {
   float* x;            // [*, H] residual stream, updated in place when p1/p2 given
@@ -96,6 +101,12 @@ struct NormArgs {
   const float* row_m2;
   const float* gate_w;
   float* gate_out;
+  // groups > 1 (RMS norm only): the row is split into `groups` equal consecutive parts, each divided
+  // by its own root mean square.  plain != 0: no norm at all, y = the updated row (the input of a
+  // projection that reads the residual stream itself).  y may be null with y_f32 set (fp32 output
+  // only; y_f32 == x normalises the stream in place).
+  int groups;
+  int plain;
 };
 cudaError_t launch_norm(cudaStream_t st, const NormArgs& a);
 
@@ -106,6 +117,10 @@ cudaError_t launch_norm(cudaStream_t st, const NormArgs& a);
 // swiglu == 2: out[t,j] = relu(h[t,j])^2
 cudaError_t launch_act(cudaStream_t st, int odt, int T, int F, const float* h, int S, size_t stride,
                        const float* bias, int swiglu, void* out, float glu_limit = 0.f);
+// Per-layer token input: out[t, j] = gelu_tanh(sum_s h[s][t][j]) * table[tokens[t]][col0 + j] for j < n,
+// zero for n <= j < ld_out (h rows ld_h apart, table rows ld_table apart in the weight dtype)
+cudaError_t launch_token_gate(cudaStream_t st, int odt, int wdt, int T, int n, const float* h, int S, size_t stride, int ld_h,
+                              const int* tokens, const void* table, int ld_table, int col0, void* out, int ld_out);
 
 // Sum split-K partials (+bias), RoPE rotate_half on Q and K (rope.go:153-205), write Q
 // [T, nh*hd] (dtype qdt) and scatter K,V into the paged pool (dtype kvdt) at slots[t].
@@ -437,6 +452,27 @@ struct WinAttnArgs {
   const int* block_tables; int max_blocks;
   const int *cu_q, *seq_start, *seq_len, *tile_seq, *tile_q0;  // without a tile list: one query per sequence at seq_len - 1
   int n_tiles, qtile;
+  // ---- further options (all off when zero / null)
+  // projection epilogue: qk_norm 3 = per-head RMS norm times a weight [dim] shared by the heads;
+  // rotation of the first 2 rot_half entries of every q / k head BEFORE the norm (pairs (2i, 2i + 1)
+  // when rot_pairs, else (i, i + rot_half)); q of head h at position p times
+  // (1 + qtemp_coef ln(floor((p + 1) / qtemp_every) + 1)) * head_scale[h]; values mixed with those an
+  // earlier layer left in vfirst ([T, G vdim] fp32): v <- (1 - *vmix) v + *vmix vfirst, or (vfirst_write)
+  // the layer's own values stored there; gate_out [T, H] = sigmoid of the H columns after Q | K | V
+  const float *qnorm_w, *knorm_w;
+  int rot_half, rot_pairs;
+  const float *cosT, *sinT;     // [T, rot_half] of the step's rows
+  const int* positions;         // [T]
+  float qtemp_coef; int qtemp_every;
+  const float* head_scale;      // [H]
+  const float* vmix;            // [1] on the device
+  float* vfirst; int vfirst_write;
+  float* gate_out;
+  // attention: score(i, j) -= 2^(-slope_exp (h + 1) / H) (i - j); the sink's score is sink_w[h] instead of 0;
+  // gate_head: `gate` holds one number per (token, head), gate[t * gate_ld + h]
+  float slope_exp;
+  const float* sink_w;          // [H]
+  int gate_head;
 };
 cudaError_t launch_winattn_prep(cudaStream_t st, int qdt, int kvdt, const WinAttnArgs& a);
 // Projection epilogue of an attention whose q, k, v pass a short causal convolution over time:
@@ -510,6 +546,11 @@ struct LinRecArgs {
   int onorm_ld;          // 0: one [vdim] weight shared by the heads; vdim: a weight per head
   const int *cu_q, *positions, *state_slots;  // [n_seqs + 1], [T], [n_seqs]
   float* state_pool; size_t slot_floats, state_off;  // this layer's [H][dim][vdim] inside a slot
+  // scan only: qk_div > 1 — q and k belong to groups of qk_div neighbouring heads (head h reads rows
+  // (h / qk_div) * dim ...); decay_p != null — one decay per (token, head), decay_p[t * decay_ld + h],
+  // instead of one per key entry
+  int qk_div;
+  const float* decay_p; int decay_ld;
   float* qkw;            // [T, 3 H dim]: q | k | decay
   float* vv;             // [T, H vdim]
   float* o;              // [T, H vdim] read-outs
@@ -527,6 +568,11 @@ constexpr int LINREC_MAX_DIM = 256;
 cudaError_t launch_token_shift(cudaStream_t st, int adt, int T, int n_seqs, int W, int n_mix, const void* h,
                                const float* mu, const int* cu_q, const int* positions, const int* state_slots,
                                const float* state_pool, size_t slot_floats, size_t tail_off, void* out);
+// What a mixer reads: out[t] = h[t] + sum_j w[:, j] h[t - taps + 1 + j] per channel (h fp32 [T, W], w [W, taps],
+// out act dtype); rows before a step's first one come from the slot's tail [taps - 1][W], zeros before position 0.
+cudaError_t launch_mixer_conv(cudaStream_t st, int adt, int T, int n_seqs, int W, int taps, const float* h, const float* w,
+                              const int* cu_q, const int* positions, const int* state_slots, const float* state_pool,
+                              size_t slot_floats, size_t tail_off, void* out);
 // After a step: the last taps - 1 inputs of every sequence become its slot's tail [taps - 1][channels].
 // Source: split-K partials (+ bias) when seg.p, else rows of `act` (act dtype, row stride channels).
 struct TailJob {
@@ -560,6 +606,28 @@ struct MambaArgs {
   int n_mamba, layer;  // Mamba2 layers in the model, index of this one among them
 };
 cudaError_t launch_mamba_conv(cudaStream_t st, const MambaArgs& a);
+// Mamba-2 of a model given as a list of layers: state and convolution tail live in the sequence's
+// state slot, the scan is the linear-recurrence scan of linrec.cu (k = B, q = C of the head's group,
+// v = dt x, one decay exp(-exp(A_log) dt) per token and head).
+struct Mamba2SlotArgs {
+  int T, n_seqs;
+  int heads, vdim, N, G, taps;  // inner = heads vdim, convolution channels = inner + 2 G N
+  int norm_groups;
+  float eps;
+  int fast_act;                 // SiLU through fast intrinsics (the bf16 serving mode)
+  // input projection [z (inner) | x (inner) | B (G N) | C (G N) | dt (heads)]: split-K partials [S][T][in_ld]
+  const float* in_p; int in_S; size_t in_stride; int in_ld;
+  const float *conv_w, *conv_b, *dt_bias, *a_log, *d_skip, *norm_w;  // [ch, taps], [ch], [heads] x 3, [inner]
+  const int *cu_q, *positions, *state_slots;
+  const float* state_pool; size_t slot_floats, tail_off;  // tail [taps - 1][ch] inside a slot
+  float* xbc;     // [T, ch]   silu(conv + bias): x | B | C
+  float* dtx;     // [T, inner] dt * x (the scan's values)
+  float* decay;   // [T, heads]
+  const float* o; // [T, inner] the scan's read-outs
+  void* out; int o_ld;  // [T, o_ld] act dtype: input of the output projection
+};
+cudaError_t launch_mamba2_slot_prep(cudaStream_t st, const Mamba2SlotArgs& a);
+cudaError_t launch_mamba2_slot_out(cudaStream_t st, int odt, const Mamba2SlotArgs& a);
 cudaError_t launch_mamba_scan(cudaStream_t st, const MambaArgs& a);
 cudaError_t launch_mamba_gate_norm(cudaStream_t st, const MambaArgs& a, int odt, void* out);
 

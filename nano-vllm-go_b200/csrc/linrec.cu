@@ -65,6 +65,7 @@ __device__ __forceinline__ void lr_cp_async4(uint32_t dst, const void* src, bool
 // at a time, in registers) for all TT tokens, whose inner vectors sit in shared memory and are
 // read as broadcasts — the matrix crosses L2 once per TT tokens instead of once per token.
 constexpr int LP_RC = 16;  // inner entries per register chunk
+constexpr int TAIL_MAX_TAPS_C = 8;  // most taps of a short convolution
 
 template <int TT>
 __global__ void __launch_bounds__(256) linrec_prep_kernel(LinRecArgs a, Trace tr) {
@@ -211,12 +212,15 @@ __global__ void __launch_bounds__(32 * NW) linrec_scan_kernel(LinRecArgs a, Trac
   const size_t part_ld[3] = {direct ? (size_t)a.q.ld : (size_t)3 * hd, direct ? (size_t)a.k.ld : (size_t)3 * hd, (size_t)3 * hd};
   const float* v_p = direct ? a.v.p : a.vv;
   const size_t v_ld = direct ? (size_t)a.v.ld : (size_t)hv;
+  const int qk_head = a.qk_div > 1 ? head / a.qk_div : head;
   auto load_chunk = [&](int t0, int buf) {
     const int nt = min(TC, n_new - t0);
     for (int i = tid; i < TC * 3 * DP; i += NT) {
       const int tt = i / (3 * DP), j = i % (3 * DP), pt = j / DP, r = j % DP;
       const bool ok = tt < nt && r < dim;
-      const float* src = part_p[pt] + (size_t)(r0 + t0 + (ok ? tt : 0)) * part_ld[pt] + head * dim + (ok ? r : 0);
+      const size_t trow = (size_t)(r0 + t0 + (ok ? tt : 0));
+      const float* src = (pt == 2 && a.decay_p) ? a.decay_p + trow * a.decay_ld + head
+                                                : part_p[pt] + trow * part_ld[pt] + (pt < 2 ? qk_head : head) * dim + (ok ? r : 0);
       lr_cp_async4(smem_addr(&stage[buf][tt][j]), src, ok);
     }
     for (int i = tid; i < TC * VC; i += NT) {
@@ -649,6 +653,76 @@ cudaError_t launch_token_shift(cudaStream_t st, int adt, int T, int n_seqs, int 
   else
     (void)launch_k(token_shift_kernel<bf16>, dim3(T), dim3(128), 0, st, T, n_seqs, W, n_mix, (const bf16*)h, mu, cu_q,
                    positions, state_slots, state_pool, slot_floats, tail_off, (bf16*)out, next_trace(43));
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------ convolution on a mixer's input
+// One CTA per token; TAPS > 0: the number of taps at compile time.  Where tap j's input lives is the
+// same for every channel of the row: a row of this step, a row of the slot's tail, or nowhere
+// (before the sequence's start).
+template <typename AT, int TAPS>
+__global__ void __launch_bounds__(256) mixer_conv_kernel(int T, int n_seqs, int W, int taps_rt, const float* __restrict__ h,
+                                                         const float* __restrict__ w, const int* __restrict__ cu_q,
+                                                         const int* __restrict__ positions,
+                                                         const int* __restrict__ state_slots,
+                                                         const float* __restrict__ state_pool, size_t slot_floats,
+                                                         size_t tail_off, AT* __restrict__ out, Trace tr) {
+  TRACE_ENTRY(tr);
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int MT = TAPS > 0 ? TAPS : TAIL_MAX_TAPS_C;
+  const int taps = TAPS > 0 ? TAPS : taps_rt;
+  const int t = blockIdx.x;
+  __shared__ int s_seq;
+  if (T == n_seqs) {
+    if (threadIdx.x == 0) s_seq = t;
+  } else {
+    for (int i = threadIdx.x; i < n_seqs; i += blockDim.x)
+      if (cu_q[i] <= t && t < cu_q[i + 1]) s_seq = i;
+  }
+  __syncthreads();
+  const int s = s_seq;
+  const int li = t - cu_q[s], pos = positions[t], keep = taps - 1;
+  const float* tail = state_pool + (size_t)state_slots[s] * slot_floats + tail_off;
+  const float* src[MT];
+#pragma unroll
+  for (int j = 0; j < MT; j++) {
+    src[j] = nullptr;
+    if (j < taps) {
+      const int back = keep - j;  // input `back` positions before this token
+      if (back <= li) src[j] = h + (size_t)(t - back) * W;
+      else if (back <= pos) src[j] = tail + (size_t)(keep - (back - li)) * W;
+    }
+  }
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    float u[MT], wv[MT];
+#pragma unroll
+    for (int j = 0; j < MT; j++) {  // all the loads first
+      u[j] = (j < taps && src[j]) ? src[j][c] : 0.f;
+      wv[j] = j < taps ? w[(size_t)c * taps + j] : 0.f;
+    }
+    float y = h[(size_t)t * W + c];
+#pragma unroll
+    for (int j = 0; j < MT; j++) y = fmaf(wv[j], u[j], y);
+    out[(size_t)t * W + c] = from_f32<AT>(y);
+  }
+  TRACE_EXIT(tr);
+}
+
+cudaError_t launch_mixer_conv(cudaStream_t st, int adt, int T, int n_seqs, int W, int taps, const float* h, const float* w,
+                              const int* cu_q, const int* positions, const int* state_slots, const float* state_pool,
+                              size_t slot_floats, size_t tail_off, void* out) {
+  if (T <= 0) return cudaSuccess;
+  if (taps < 1 || taps > TAIL_MAX_TAPS_C) return cudaErrorInvalidValue;
+#define MC(AT_, TP_)                                                                                                  \
+  (void)launch_k(mixer_conv_kernel<AT_, TP_>, dim3(T), dim3(256), 0, st, T, n_seqs, W, taps, h, w, cu_q, positions,    \
+                 state_slots, state_pool, slot_floats, tail_off, (AT_*)out, next_trace(43))
+  if (adt == DT_F32) {
+    if (taps == 2) MC(float, 2); else if (taps == 3) MC(float, 3); else if (taps == 4) MC(float, 4); else MC(float, 0);
+  } else {
+    if (taps == 2) MC(bf16, 2); else if (taps == 3) MC(bf16, 3); else if (taps == 4) MC(bf16, 4); else MC(bf16, 0);
+  }
+#undef MC
   return cudaGetLastError();
 }
 

@@ -153,6 +153,134 @@ mamba_gate_norm_kernel(MambaArgs a, OT* __restrict__ out, Trace tr) {
   TRACE_EXIT(tr);
 }
 
+// ------------------------------------------------------------------ Mamba-2 with state slots
+// The Mamba-2 mixer of a model given as a list of layers (forward_layered.cu).  Its state
+// S (N x vdim per head, fp32) and the last taps - 1 inputs of its convolution live in the
+// sequence's state slot; the recurrence itself runs in the linear-recurrence scan of linrec.cu.
+//   mamba2_slot_prep_kernel  one CTA per token: split-K sum of the input projection, causal convolution
+//                            over x | B | C (inputs before the step's first row from the slot's tail, zeros
+//                            before the sequence's start), + bias, SiLU; dt = softplus(dt + bias) (fp32, no
+//                            clamp), the head's decay exp(-exp(A_log) dt), and dt x (the scan's values)
+//   mamba2_slot_out_kernel   one CTA per token: y = read-out + D x, times silu(z), RMS norm in norm_groups
+//                            equal parts (eps of the model), times the weight -> act dtype
+template <int TAPS>
+__global__ void __launch_bounds__(256) mamba2_slot_prep_kernel(Mamba2SlotArgs a, Trace tr) {
+  TRACE_ENTRY(tr);
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int MT = TAPS > 0 ? TAPS : 8;
+  const int taps = TAPS > 0 ? TAPS : a.taps;
+  const int t = blockIdx.x;
+  const int inner = a.heads * a.vdim, ch = inner + 2 * a.G * a.N;
+  __shared__ int s_seq;
+  __shared__ float s_dt[256];
+  if (a.T == a.n_seqs) {
+    if (threadIdx.x == 0) s_seq = t;
+  } else {
+    for (int i = threadIdx.x; i < a.n_seqs; i += blockDim.x)
+      if (a.cu_q[i] <= t && t < a.cu_q[i + 1]) s_seq = i;
+  }
+  // step sizes and decays of the heads (at most 256 heads)
+  for (int hh = threadIdx.x; hh < a.heads; hh += blockDim.x) {
+    const float z = sum_slices(a.in_p + (size_t)t * a.in_ld + inner + ch + hh, a.in_S, a.in_stride) + a.dt_bias[hh];
+    const float dt = z > 20.f ? z : log1pf(expf(z));  // softplus; above 20 the two agree to fp32 rounding
+    s_dt[hh] = dt;
+    a.decay[(size_t)t * a.heads + hh] = expf(-expf(a.a_log[hh]) * dt);
+  }
+  __syncthreads();
+  const int s = s_seq;
+  const int li = t - a.cu_q[s], pos = a.positions[t], keep = taps - 1;
+  const float* tail = a.state_pool + (size_t)a.state_slots[s] * a.slot_floats + a.tail_off;
+  const float* src[MT];
+  bool part[MT];  // the row is one of this step's partials (slices to sum)
+#pragma unroll
+  for (int j = 0; j < MT; j++) {
+    src[j] = nullptr;
+    part[j] = false;
+    if (j < taps) {
+      const int back = keep - j;
+      if (back <= li) { src[j] = a.in_p + (size_t)(t - back) * a.in_ld + inner; part[j] = true; }
+      else if (back <= pos) src[j] = tail + (size_t)(keep - (back - li)) * ch;
+    }
+  }
+  const bool one = a.in_S == 1;
+  for (int c = threadIdx.x; c < ch; c += blockDim.x) {
+    float u[MT], wv[MT];
+#pragma unroll
+    for (int j = 0; j < MT; j++) {
+      u[j] = 0.f;
+      wv[j] = j < taps ? a.conv_w[(size_t)c * taps + j] : 0.f;
+      if (j < taps && src[j]) u[j] = (one || !part[j]) ? src[j][c] : sum_slices(src[j] + c, a.in_S, a.in_stride);
+    }
+    float y = a.conv_b ? a.conv_b[c] : 0.f;
+#pragma unroll
+    for (int j = 0; j < MT; j++) y = fmaf(wv[j], u[j], y);
+    const float v = a.fast_act ? __fdividef(y, 1.0f + __expf(-y)) : silu(y);
+    a.xbc[(size_t)t * ch + c] = v;
+    if (c < inner) a.dtx[(size_t)t * inner + c] = v * s_dt[c / a.vdim];
+  }
+  TRACE_EXIT(tr);
+}
+
+template <typename OT>
+__global__ void __launch_bounds__(256) mamba2_slot_out_kernel(Mamba2SlotArgs a, Trace tr) {
+  TRACE_ENTRY(tr);
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float row[];
+  __shared__ float ginv[64];
+  const int t = blockIdx.x;
+  const int inner = a.heads * a.vdim, ch = inner + 2 * a.G * a.N;
+  for (int i = threadIdx.x; i < inner; i += blockDim.x) {
+    const float z = sum_slices(a.in_p + (size_t)t * a.in_ld + i, a.in_S, a.in_stride);
+    const float x = a.xbc[(size_t)t * ch + i];
+    const float y = a.o[(size_t)t * inner + i] + a.d_skip[i / a.vdim] * x;
+    row[i] = y * (a.fast_act ? __fdividef(z, 1.0f + __expf(-z)) : silu(z));
+  }
+  __syncthreads();
+  const int part = inner / a.norm_groups;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (int g = warp; g < a.norm_groups; g += nw) {
+    float sq = 0.f;
+    for (int i = lane; i < part; i += 32) {
+      const float v = row[g * part + i];
+      sq = fmaf(v, v, sq);
+    }
+    sq = warp_sum(sq);
+    if (lane == 0) ginv[g] = 1.0f / sqrtf(sq / (float)part + a.eps);
+  }
+  __syncthreads();
+  OT* op = (OT*)a.out + (size_t)t * a.o_ld;
+  for (int i = threadIdx.x; i < a.o_ld; i += blockDim.x)
+    op[i] = from_f32<OT>(i < inner ? row[i] * ginv[i / part] * a.norm_w[i] : 0.f);
+  TRACE_EXIT(tr);
+}
+
+cudaError_t launch_mamba2_slot_prep(cudaStream_t st, const Mamba2SlotArgs& a) {
+  if (a.T <= 0) return cudaSuccess;
+  if (a.taps < 1 || a.taps > 8 || a.heads > 256) return cudaErrorInvalidValue;
+  if (a.taps == 2) (void)launch_k(mamba2_slot_prep_kernel<2>, dim3(a.T), dim3(256), 0, st, a, next_trace(20));
+  else if (a.taps == 3) (void)launch_k(mamba2_slot_prep_kernel<3>, dim3(a.T), dim3(256), 0, st, a, next_trace(20));
+  else if (a.taps == 4) (void)launch_k(mamba2_slot_prep_kernel<4>, dim3(a.T), dim3(256), 0, st, a, next_trace(20));
+  else (void)launch_k(mamba2_slot_prep_kernel<0>, dim3(a.T), dim3(256), 0, st, a, next_trace(20));
+  return cudaGetLastError();
+}
+
+cudaError_t launch_mamba2_slot_out(cudaStream_t st, int odt, const Mamba2SlotArgs& a) {
+  if (a.T <= 0) return cudaSuccess;
+  const int inner = a.heads * a.vdim;
+  if (a.norm_groups < 1 || a.norm_groups > 64 || inner % a.norm_groups) return cudaErrorInvalidValue;
+  const size_t smem = (size_t)inner * sizeof(float);
+  if (odt == DT_F32) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(mamba2_slot_out_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    (void)launch_k(mamba2_slot_out_kernel<float>, dim3(a.T), dim3(256), smem, st, a, next_trace(22));
+  } else {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(mamba2_slot_out_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    (void)launch_k(mamba2_slot_out_kernel<bf16>, dim3(a.T), dim3(256), smem, st, a, next_trace(22));
+  }
+  return cudaGetLastError();
+}
+
 cudaError_t launch_mamba_conv(cudaStream_t st, const MambaArgs& a) {
   if (a.T <= 0) return cudaSuccess;
   (void)launch_k(mamba_conv_kernel, dim3(a.T, ceil_div(a.conv, 256)), dim3(256), 0, st, a, next_trace(20));

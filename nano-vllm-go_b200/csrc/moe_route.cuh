@@ -83,23 +83,37 @@ __device__ __forceinline__ void moe_route_row(const float* y, const float* __res
     for (int e = lane; e < E; e += 32) probs[e] = probs[e] / sum;
     __syncwarp();
   }
-  // group-limited choice: a group scores as its best expert; group g stays iff fewer than
-  // `keep` groups beat it (higher score, or equal score and lower index).  Experts of the other
-  // groups are taken out of the selection below (their probabilities are not needed again).
+  // The choice may go by other numbers than the weights: ch[e] = probs[e] + correction[e] (any sign;
+  // an expert taken out of the choice is -inf), while the weights stay probs[e].
+  __shared__ float chs[MOE_MAX_E];
+  const bool corr = ro.correction != nullptr;
+  float* ch = corr ? chs : probs;
+  const float OUT = corr ? -INFINITY : -2.f;   // marks an expert that cannot be chosen (plain scores are >= 0)
+  if (corr) {
+    for (int e = lane; e < E; e += 32) chs[e] = probs[e] + ro.correction[e];
+    __syncwarp();
+  }
+  // group-limited choice: a group scores as its best expert (or the sum of its two best); group g
+  // stays iff fewer than `keep` groups beat it (higher score, or equal score and lower index).
+  // Experts of the other groups are taken out of the selection below.
   if (ro.groups > 1 && ro.keep < ro.groups) {
     __shared__ float gsc[MOE_MAX_E];
     const int per = E / ro.groups;
     for (int g = lane; g < ro.groups; g += 32) {
-      float b = -1.f;
-      for (int j = 0; j < per; j++) b = fmaxf(b, probs[g * per + j]);
-      gsc[g] = b;
+      float b1 = -INFINITY, b2 = -INFINITY;
+      for (int j = 0; j < per; j++) {
+        const float v = ch[g * per + j];
+        if (v > b1) { b2 = b1; b1 = v; }
+        else if (v > b2) b2 = v;
+      }
+      gsc[g] = (ro.group_top2 && per > 1) ? b1 + b2 : b1;
     }
     __syncwarp();
     for (int g = lane; g < ro.groups; g += 32) {
       int beat = 0;
       for (int o = 0; o < ro.groups; o++) beat += (gsc[o] > gsc[g] || (gsc[o] == gsc[g] && o < g)) ? 1 : 0;
       if (beat >= ro.keep)
-        for (int j = 0; j < per; j++) probs[g * per + j] = -2.f;
+        for (int j = 0; j < per; j++) ch[g * per + j] = OUT;
     }
     __syncwarp();
   }
@@ -107,30 +121,40 @@ __device__ __forceinline__ void moe_route_row(const float* y, const float* __res
   int sel_i = 0;
   float ksum = 0.f;
   for (int s = 0; s < k; s++) {
-    float bv = -1.f;
+    float bv = OUT;
     int bi = 0x7fffffff;
     for (int e = lane; e < E; e += 32) {
-      float p = probs[e];
+      float p = ch[e];
       if (p > bv) {
         bv = p;
         bi = e;
       }
     }
-    // warp arg-max in two redux operations instead of five shuffle rounds: probabilities are
-    // >= 0, so their bit patterns order like the values (+1 keeps a genuine 0.0 above the -1 of
-    // a lane with no candidate); ties go to the lower expert index
-    const unsigned key = bv < 0.f ? 0u : __float_as_uint(bv) + 1u;
-    const unsigned kmax = __reduce_max_sync(0xffffffffu, key);
-    bi = (int)__reduce_min_sync(0xffffffffu, key == kmax ? (unsigned)bi : 0x7fffffffu);
-    bv = kmax ? __uint_as_float(kmax - 1u) : -1.f;
+    if (corr) {
+      // signed choice scores: order-preserving map of the float's bits to unsigned (-inf lowest)
+      const unsigned u = __float_as_uint(bv);
+      const unsigned key = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+      const unsigned kmax = __reduce_max_sync(0xffffffffu, key);
+      bi = (int)__reduce_min_sync(0xffffffffu, (key == kmax && bi != 0x7fffffff) ? (unsigned)bi : 0x7fffffffu);
+      bv = probs[bi];  // the weight comes from the score itself
+    } else {
+      // warp arg-max in two redux operations instead of five shuffle rounds: probabilities are
+      // >= 0, so their bit patterns order like the values (+1 keeps a genuine 0.0 above the -1 of
+      // a lane with no candidate); ties go to the lower expert index
+      const unsigned key = bv < 0.f ? 0u : __float_as_uint(bv) + 1u;
+      const unsigned kmax = __reduce_max_sync(0xffffffffu, key);
+      bi = (int)__reduce_min_sync(0xffffffffu, key == kmax ? (unsigned)bi : 0x7fffffffu);
+      bv = kmax ? __uint_as_float(kmax - 1u) : -1.f;
+    }
     if (lane == s) {
       sel_p = bv;
       sel_i = bi;
     }
     ksum += bv;  // moe.go:98-103: sum in descending order
-    if (lane == 0) probs[bi] = -2.f;
+    if (lane == 0) ch[bi] = OUT;
     __syncwarp();
   }
+  if (ro.sigmoid && !ro.raw) ksum += 1e-20f;
   if (lane < k) {
     topk_idx[t * k + lane] = sel_i;
     const float wgt = ro.raw ? sel_p * ro.scale : sel_p / ksum;

@@ -335,7 +335,7 @@ struct Loader {
 
 int load_safetensors(nvllm_handle* h, const char* dir, int arch, uint64_t* bytes_out, int* tensors_out) {
   if (h->finalized) return set_err(h, NVLLM_ERR_STATE, "load_safetensors after finalize");
-  if (arch == NVLLM_ARCH_DUGOPEL || arch == NVLLM_ARCH_ZOZONEX || arch == NVLLM_ARCH_LAZOVIK) {
+  if (arch == NVLLM_ARCH_DUGOPEL || arch == NVLLM_ARCH_ZOZONEX || arch == NVLLM_ARCH_LAZOVIK || arch == NVLLM_ARCH_SUTUVIK) {
     // a layered handle knows every tensor by the file's own names; finalize reports what is missing
     if (!h->layered) return set_err(h, NVLLM_ERR_INVALID, "this checkpoint family needs a handle of nvllm_create_layered");
     Checkpoint ck;
