@@ -615,6 +615,85 @@ def zozonex_moe_width():
     return zozonex_cfg(1024, 24, 49155, 8, 8, 64, 128, 4, 16, 4, 64, 1024, 4096)
 
 
+def sutuvik_cfg(width, n_layers, vocab, m_heads, m_vdim, m_state, m_groups, conv, a_heads, a_kv, a_dim, a_vdim, b_dim,
+                experts, top, ff, groups, keep, parts, taps, side):
+    """Mamba-2 layers with every third layer an attention layer, the two attention kinds in turn
+    (distance penalty + learned sink + head gates; rotated pairs + capped scores), all of them mixing
+    values with the first one's; gated experts chosen within the best groups in every layer; norms in
+    `parts` parts, `taps` taps on what the mixers read, a token input of `side` entries per layer."""
+    layers = []
+    moe = dict(mlp=C.MLP_MOE, act=C.FFN_SWIGLU, ff=ff, experts=experts, top=top, groups=groups, keep_groups=keep,
+               route_sigmoid=1, route_correction=1, group_top2=1, route_norm=1)
+    n_att = 0
+    for l in range(n_layers):
+        if l % 3 == 2:
+            kw = dict(mixer=C.MIXER_ATTENTION, heads=a_heads, kv_heads=a_kv, vdim=a_vdim, sink=1, v_mix=1)
+            if n_att % 2 == 0:
+                kw.update(dim=a_dim, scale=float(a_dim ** -0.5), qk_norm=3, dist_slope=C.SUTUVIK_SLOPE_EXPONENT, sink_learned=1,
+                          head_gate=1, qtemp_coef=0.5, qtemp_every=1024)
+            else:
+                kw.update(dim=b_dim, scale=float(b_dim ** -0.5), qk_norm=1, head_temp=1, softcap=30.0, rot_pairs=1,
+                          rot_dims=b_dim // 2, rot_base=500000.0, rot_piecewise=1, rot_factor=8.0, rot_original=8192.0,
+                          rot_fast=4.0, rot_slow=1.0)
+            n_att += 1
+        else:
+            kw = dict(mixer=C.MIXER_MAMBA2, heads=m_heads, vdim=m_vdim, dim=m_state, state=m_state, ssm_groups=m_groups,
+                      norm_groups=m_groups, conv=conv)
+        layers.append(C.LayerSpec(**kw, **moe))
+    return C.ListedModelConfig("sutuvik", vocab, width, tuple(layers), 1e-5, arch=C.ARCH_SUTUVIK,
+                               block_style=C.LBLOCK_SEQUENTIAL_PRENORM, tied_head=True, norm_groups=parts, embed_norm=True,
+                               mixer_conv=taps, side_dim=side, logit_scale=0.5)
+
+
+def sutuvik_device_weights(cfg, device, seed=1234):
+    import torch
+    g = torch.Generator(device=f"cuda:{device}")
+    for i, (name, shape) in enumerate(cfg.tensor_shapes().items()):
+        g.manual_seed(seed * 1000003 + i)
+        t = torch.empty(shape, dtype=torch.float32, device=f"cuda:{device}")
+        if name.endswith(".A_log"):
+            t.uniform_(-3.0, 0.5, generator=g)
+        elif name.endswith(".dt_bias"):
+            t.uniform_(-3.0, 0.0, generator=g)
+        elif name.endswith(".vmix"):
+            t.fill_(0.5)
+        elif name.endswith(".sink") or name.endswith(".correction") or name.endswith(".conv.b"):
+            t.normal_(0.0, 0.1, generator=g)
+        elif len(shape) == 1:
+            t.normal_(1.0, 0.02, generator=g)       # norm weights, per-head multipliers, skips
+        elif name.endswith(".conv") or name.endswith(".canon1"):
+            t.normal_(0.0, shape[1] ** -0.5, generator=g)
+        else:
+            t.normal_(0.0, 0.02 if name in ("embed", "side.embed") else shape[1] ** -0.5, generator=g)
+        yield name, t.to(torch.bfloat16).view(torch.int16).cpu().numpy().view(np.uint16)
+        del t
+
+
+# width 1024, 24 layers like Granite-MoE-1B: 16 Mamba-2 layers (32 heads of 64, state 128, 4 taps) and 8 attention
+# layers (16 heads over 4 K / V heads of 64 values; keys of 64 in the biased kind, of 128 with 64 rotated in the
+# other); 32 gated experts of 512 in 4 groups, 8 per token from the best 2 groups (Granite's expert sizes);
+# norms in 2 parts, 4 taps on the mixers' input, 64 token-input entries per layer.
+def _su():
+    return sutuvik_cfg(1024, 24, 49155, 32, 64, 128, 1, 4, 16, 4, 64, 64, 128, 32, 8, 512, 4, 2, 2, 4, 64)
+
+
+SUTUVIK_SIZES = {
+    "su-1b": (_su, "granite-moe-1b", 128, 128, 128),
+    "su-1b-long": (_su, "granite-moe-1b", 16, 4096, 64),
+    "su-1b-batch": (_su, "granite-moe-1b", 64, 512, 128),
+}
+
+
+def hybrid_moe_width():
+    """Mamba2 and attention blocks (every third) at the width, depth and mixer sizes of the sizes
+    above: the library's other model with Mamba-2's convolution, scan and gated norm."""
+    from dataclasses import replace
+    cfg = C.tiny_hybrid(vocab_size=49155, hidden=1024, num_layers=24, num_heads=16, num_kv_heads=4, head_dim=64,
+                        ffn_dim=4096, max_seq_len=8192, mamba_num_heads=32, mamba_head_dim=64, mamba_state_size=128,
+                        mamba_n_groups=1, mamba_conv_kernel=4, hybrid_layers=tuple(l % 3 != 2 for l in range(24)))
+    return replace(cfg, name="hybrid-mamba2-w1024")
+
+
 DESIGN_SIZES = {
     # name: (layer-listed config, closest uniform preset, batch, prompt, decode steps)
     "dense-1b": (lambda: dugopel_cfg(2048, 16, 32, 64, 32, 64, 128, 768, 8192, 128256), "llama-3.2-1b", 64, 512, 128),
@@ -637,8 +716,9 @@ def design_bench(args):
     peaks = load_peaks()
     R = nvllm_pkg.sub("runner")
     design = args.design
-    sizes = {"zozonex": ZOZONEX_SIZES, "lazovik": LAZOVIK_SIZES}.get(design, DESIGN_SIZES)
-    gen = {"zozonex": zozonex_device_weights, "lazovik": lazovik_device_weights}.get(design, dugopel_device_weights)
+    sizes = {"zozonex": ZOZONEX_SIZES, "lazovik": LAZOVIK_SIZES, "sutuvik": SUTUVIK_SIZES}.get(design, DESIGN_SIZES)
+    gen = {"zozonex": zozonex_device_weights, "lazovik": lazovik_device_weights,
+           "sutuvik": sutuvik_device_weights}.get(design, dugopel_device_weights)
     out = {"design": design, "dtype": "bf16", "data": "synthetic (random-init weights, random prompts)",
            "steps": args.steps, "warmup": args.warmup, "peaks": peaks, "sizes": {}}
     names = [n for n in sizes if args.design_size in (None, n)]
@@ -648,9 +728,11 @@ def design_bench(args):
         others = (base_name, "hybrid-mamba2-1b") if design == "zozonex" and not args.no_hybrid else (base_name,)
         if design == "lazovik" and not args.no_hybrid:
             others = (base_name, "zozonex-1b")
+        if design == "sutuvik" and not args.no_hybrid:
+            others = (base_name, "hybrid-mamba2-w1024")
         for which in (design,) + others:
             cfg = mk() if which == design else hybrid_1b() if which == "hybrid-mamba2-1b" else \
-                zozonex_moe_width() if which == "zozonex-1b" else C.PRESETS[base_name]()
+                hybrid_moe_width() if which == "hybrid-mamba2-w1024" else zozonex_moe_width() if which == "zozonex-1b" else C.PRESETS[base_name]()
             if which != design and hasattr(cfg, "max_seq_len") and cfg.max_seq_len < P + D + 1:
                 from dataclasses import replace
                 cfg = replace(cfg, max_seq_len=P + D + 32)
@@ -742,12 +824,12 @@ def main():
     ap.add_argument("--no-profile", action="store_true")
     ap.add_argument("--no-tp", action="store_true",
                     help="skip the Falcon-7B tensor-parallel leg (configs[3] at tp = --gpus)")
-    ap.add_argument("--design", default=None, choices=["dugopel", "zozonex", "lazovik"],
+    ap.add_argument("--design", default=None, choices=["dugopel", "zozonex", "lazovik", "sutuvik"],
                     help="instead of the default workload: the layer-listed design beside the closest "
                          "uniform model at equal size (prefill and decode, per-kernel roofline)")
     ap.add_argument("--no-hybrid", action="store_true",
-                    help="--design zozonex / lazovik: skip the second baseline (Mamba2 hybrid / Zozonex at equal width)")
-    ap.add_argument("--design-size", default=None, choices=sorted(DESIGN_SIZES) + sorted(ZOZONEX_SIZES) + sorted(LAZOVIK_SIZES))
+                    help="--design zozonex / lazovik / sutuvik: skip the second baseline (Mamba2 hybrid / Zozonex at equal width)")
+    ap.add_argument("--design-size", default=None, choices=sorted(DESIGN_SIZES) + sorted(ZOZONEX_SIZES) + sorted(LAZOVIK_SIZES) + sorted(SUTUVIK_SIZES))
     args = ap.parse_args()
     if args.design:
         return design_bench(args)

@@ -1036,6 +1036,7 @@ __global__ void __launch_bounds__(128) winattn_mma_kernel(WinAttnArgs a, Trace t
 // on its keys, the running softmax in base 2, O += P V — and the four partial states meet in
 // shared memory at the end, where the sink joins once.
 constexpr int WDM_ST = 3;
+constexpr int WDM_MIN_TILES = 4;  // a split range holds at least this many key tiles
 
 template <int DIM, int VDIM>
 __global__ void __launch_bounds__(128) winattn_decode_mma_kernel(WinAttnArgs a, Trace tr) {
@@ -1054,6 +1055,15 @@ __global__ void __launch_bounds__(128) winattn_decode_mma_kernel(WinAttnArgs a, 
   const int k_lo = first_key(a, qp);
   const int t_lo = k_lo / WM_K * WM_K;
   const int n_kt = (qp + 1 - t_lo + WM_K - 1) / WM_K;
+  // the CTA's range of key tiles: all of them, or (long contexts, few sequences) one of n_split ranges of at
+  // least WDM_MIN_TILES tiles; a range past the context is empty and hands in an empty state
+  const int n_split = a.n_split > 1 ? a.n_split : 1;
+  int kt_b = 0, kt_e = n_kt;
+  if (n_split > 1) {
+    const int per = max(WDM_MIN_TILES, (n_kt + n_split - 1) / n_split);
+    kt_b = min(n_kt, (int)blockIdx.z * per);
+    kt_e = min(n_kt, kt_b + per);
+  }
   const int* bt = a.block_tables + (size_t)seq * a.max_blocks;
   const bf16* kpool = (const bf16*)a.kpool;
   const bf16* vpool = (const bf16*)a.vpool;
@@ -1081,9 +1091,9 @@ __global__ void __launch_bounds__(128) winattn_decode_mma_kernel(WinAttnArgs a, 
       cp_async16(smem_addr(vd + r * VP + c * 8), ok ? (const void*)(vpool + (kb + r) * VDIM + c * 8) : (const void*)vpool, ok);
     }
   };
-  load_kv(0);
+  if (kt_b < kt_e) load_kv(kt_b);
   cp_async_commit();
-  if (n_kt > 1) load_kv(1);
+  if (kt_b + 1 < kt_e) load_kv(kt_b + 1);
   cp_async_commit();
 
   const int gid = lane >> 2, tig = lane & 3;
@@ -1098,12 +1108,12 @@ __global__ void __launch_bounds__(128) winattn_decode_mma_kernel(WinAttnArgs a, 
   const float slope_lo = gid < GQ ? head_slope(a, h0 + gid) * 1.4426950408889634f : 0.f;
   const float slope_hi = gid + 8 < GQ ? head_slope(a, h0 + gid + 8) * 1.4426950408889634f : 0.f;
 
-  for (int kt = 0; kt < n_kt; kt++) {
-    if (kt + 2 < n_kt) load_kv(kt + 2);
+  for (int kt = kt_b; kt < kt_e; kt++) {
+    if (kt + 2 < kt_e) load_kv(kt + 2);
     cp_async_commit();
     cp_async_wait<2>();  // tile kt (and, the first time, the queries) has landed
     __syncthreads();
-    if (kt == 0) {
+    if (kt == kt_b) {
 #pragma unroll
       for (int kk = 0; kk < DIM / 16; kk++)
         ldsm_x4(smem_addr(Qs + (lane & 15) * DP + kk * 16 + (lane >> 4) * 8), qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3]);
@@ -1197,22 +1207,76 @@ __global__ void __launch_bounds__(128) winattn_decode_mma_kernel(WinAttnArgs a, 
     }
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < GQ * VDIM; i += blockDim.x) {
-    const int r = i / VDIM, col = i % VDIM;
-    const float sk = sink_score(a, h0 + r) * 1.4426950408889634f;
-    float mt = a.sink ? sk : -INFINITY;
-    for (int w = 0; w < 4; w++) mt = fmaxf(mt, mrg[((size_t)w * 16 + r) * MS + VDIM]);
-    float lt = a.sink ? exp2f(sk - mt) : 0.f, v = 0.f;
-    for (int w = 0; w < 4; w++) {
-      const float* pw = mrg + ((size_t)w * 16 + r) * MS;
-      const float cw = exp2f(pw[VDIM] - mt);  // a warp that saw no key has max -inf: weight 0
-      lt += pw[VDIM + 1] * cw;
-      v += pw[col] * cw;
+  if (n_split > 1) {
+    // the CTA's state (relative to its own maximum, without the sink) goes to its place among the pair's
+    // n_split; the CTA that arrives last adds them up.  Nobody waits: the counter only tells who is last.
+    __shared__ int is_last;
+    const size_t pair = (size_t)seq * a.G + g;
+    float* part = a.split_ws + (pair * n_split + blockIdx.z) * 16 * MS;
+    for (int i = threadIdx.x; i < GQ * VDIM; i += blockDim.x) {
+      const int r = i / VDIM, col = i % VDIM;
+      float mt = -INFINITY;
+      for (int w = 0; w < 4; w++) mt = fmaxf(mt, mrg[((size_t)w * 16 + r) * MS + VDIM]);
+      float lt = 0.f, v = 0.f;
+      if (mt > -INFINITY) {
+        for (int w = 0; w < 4; w++) {
+          const float* pw = mrg + ((size_t)w * 16 + r) * MS;
+          const float cw = exp2f(pw[VDIM] - mt);
+          lt += pw[VDIM + 1] * cw;
+          v += pw[col] * cw;
+        }
+      }
+      part[(size_t)r * MS + col] = v;
+      if (col == 0) {
+        part[(size_t)r * MS + VDIM] = mt;
+        part[(size_t)r * MS + VDIM + 1] = lt;
+      }
     }
-    if (a.gate) v *= gate_row(a, (size_t)seq, h0 + r, VDIM)[a.gate_head ? 0 : col];
-    ((bf16*)a.out)[(size_t)seq * a.o_ld + (size_t)(h0 + r) * VDIM + col] = __float2bfloat16_rn(v / lt);
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const unsigned before = atomicAdd(a.split_cnt + pair, 1u);
+      is_last = before == (unsigned)n_split - 1;
+      if (is_last) a.split_cnt[pair] = 0;  // every CTA of the pair has arrived: zero again for the next launch
+    }
+    __syncthreads();
+    if (is_last) {
+      __threadfence();
+      const float* all = a.split_ws + pair * n_split * 16 * MS;
+      for (int i = threadIdx.x; i < GQ * VDIM; i += blockDim.x) {
+        const int r = i / VDIM, col = i % VDIM;
+        const float sk = sink_score(a, h0 + r) * 1.4426950408889634f;
+        float mt = a.sink ? sk : -INFINITY;
+        for (int z = 0; z < n_split; z++) mt = fmaxf(mt, __ldcg(all + ((size_t)z * 16 + r) * MS + VDIM));
+        float lt = a.sink ? exp2f(sk - mt) : 0.f, v = 0.f;
+        for (int z = 0; z < n_split; z++) {
+          const float* pz = all + ((size_t)z * 16 + r) * MS;
+          const float cz = exp2f(__ldcg(pz + VDIM) - mt);  // an empty range has max -inf: weight 0
+          lt += __ldcg(pz + VDIM + 1) * cz;
+          v += __ldcg(pz + col) * cz;
+        }
+        if (a.gate) v *= gate_row(a, (size_t)seq, h0 + r, VDIM)[a.gate_head ? 0 : col];
+        ((bf16*)a.out)[(size_t)seq * a.o_ld + (size_t)(h0 + r) * VDIM + col] = __float2bfloat16_rn(v / lt);
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < GQ * VDIM; i += blockDim.x) {
+      const int r = i / VDIM, col = i % VDIM;
+      const float sk = sink_score(a, h0 + r) * 1.4426950408889634f;
+      float mt = a.sink ? sk : -INFINITY;
+      for (int w = 0; w < 4; w++) mt = fmaxf(mt, mrg[((size_t)w * 16 + r) * MS + VDIM]);
+      float lt = a.sink ? exp2f(sk - mt) : 0.f, v = 0.f;
+      for (int w = 0; w < 4; w++) {
+        const float* pw = mrg + ((size_t)w * 16 + r) * MS;
+        const float cw = exp2f(pw[VDIM] - mt);  // a warp that saw no key has max -inf: weight 0
+        lt += pw[VDIM + 1] * cw;
+        v += pw[col] * cw;
+      }
+      if (a.gate) v *= gate_row(a, (size_t)seq, h0 + r, VDIM)[a.gate_head ? 0 : col];
+      ((bf16*)a.out)[(size_t)seq * a.o_ld + (size_t)(h0 + r) * VDIM + col] = __float2bfloat16_rn(v / lt);
+    }
   }
-  if (g == 0)
+  if (g == 0 && blockIdx.z == 0)
     for (int col = a.H * VDIM + threadIdx.x; col < a.o_ld; col += blockDim.x)
       ((bf16*)a.out)[(size_t)seq * a.o_ld + col] = __float2bfloat16_rn(0.f);
   TRACE_EXIT(tr);
@@ -1225,7 +1289,10 @@ static cudaError_t winattn_decode_mma_launch(cudaStream_t st, const WinAttnArgs&
   const size_t smem = (size_t)16 * (DIM + 8) * 2 + std::max(tiles, merge);
   if (smem > 48 * 1024)
     cudaFuncSetAttribute(winattn_decode_mma_kernel<DIM, VDIM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  (void)launch_k(winattn_decode_mma_kernel<DIM, VDIM>, dim3(a.n_tiles, a.G), dim3(128), smem, st, a, next_trace(37));
+  const int n_split = a.n_split > 1 && a.split_ws && a.split_cnt ? std::min(a.n_split, WINATTN_MAX_SPLIT) : 1;
+  WinAttnArgs b = a;
+  b.n_split = n_split;
+  (void)launch_k(winattn_decode_mma_kernel<DIM, VDIM>, dim3(a.n_tiles, a.G, n_split), dim3(128), smem, st, b, next_trace(37));
   return cudaGetLastError();
 }
 

@@ -28,7 +28,7 @@ void free_workspace(nvllm_handle* h) {
                   w.sort.counts, w.sort.offsets, w.sort.cursor, w.sort.sorted_pair, w.sort.pair_row,
                   w.sort.a_rows, w.sort.tile_expert, w.sort.tile_row0, w.sort.tile_rows,
                   w.sort.n_tiles, w.moe_Y, w.moe_y, w.moe_xs, w.lr_qkw, w.lr_v, w.lr_o, w.att_gate, w.sh_gate, w.mx_in,
-                  w.m2_xbc, w.m2_dtx, w.m2_decay, w.v_first, w.side_g};
+                  w.m2_xbc, w.m2_dtx, w.m2_decay, w.v_first, w.side_g, w.att_split, w.att_split_cnt};
   for (void* p : ptrs)
     if (p) cudaFree(p);
   for (auto& r : h->ropes) {
@@ -117,7 +117,7 @@ int ensure_workspace(nvllm_handle* h, int T, int n) {
     WS(w.dl_qkv, Tc * dch * 4);
     WS(w.dl_bg, Tc * 2 * dh * 4);
     WS(w.dl_o, Tc * dhv * 4);
-    size_t lhd = 0, lhv = 0, agate = 0, m2ch = 0, m2in = 0, m2h = 0, vfirst = 0;
+    size_t lhd = 0, lhv = 0, agate = 0, m2ch = 0, m2in = 0, m2h = 0, vfirst = 0, split_g = 0, split_v = 0;
     bool tmix = false, shared = false;
     for (auto& y : h->ll) {
       const nvllm_layer_spec& s = y.s;
@@ -129,6 +129,8 @@ int ensure_workspace(nvllm_handle* h, int T, int n) {
       } else if (s.mixer == NVLLM_MIXER_ATTENTION) {
         if (s.head_gate) agate = std::max(agate, (size_t)s.heads);
         if (s.v_mix) vfirst = std::max(vfirst, (size_t)s.kv_heads * s.vdim);
+        split_g = std::max(split_g, (size_t)s.kv_heads);
+        split_v = std::max(split_v, (size_t)s.vdim);
       } else if (s.mixer == NVLLM_MIXER_GLA) {
         lhd = std::max(lhd, (size_t)s.heads * s.dim);
         lhv = std::max(lhv, (size_t)s.heads * s.vdim);
@@ -149,6 +151,13 @@ int ensure_workspace(nvllm_handle* h, int T, int n) {
     WS(w.m2_decay, Tc * m2h * 4);
     WS(w.v_first, Tc * vfirst * 4);
     WS(w.side_g, Tc * (size_t)h->side_p * asz);
+    if (split_g) {  // decode steps have one row per sequence: nc sequences at most
+      const size_t pairs = (size_t)nc * split_g;
+      WS(w.att_split, pairs * WINATTN_MAX_SPLIT * 16 * (split_v + 2) * 4);
+      WS(w.att_split_cnt, pairs * 4);
+      NV_CHECK(h, cudaMemsetAsync(w.att_split_cnt, 0, pairs * 4, h->stream));
+      w.att_split_pairs = (int)pairs;
+    }
     if (h->mixer_conv && !h->moe) WS(w.xn_f32, Tc * H * 4);
     if (tmix) WS(w.mx_in, (size_t)5 * Tc * H * asz);
     if (shared) WS(w.sh_gate, (size_t)Tc * 4);

@@ -966,6 +966,14 @@ static int mixer_attention(nvllm_handle* h, const ListedLayer& y, int run_idx, P
     a.tile_seq = d + L.tile_seq; a.tile_q0 = d + L.tile_q0; a.n_tiles = L.n_qtiles; a.qtile = h->attn_qtile;
   } else {
     a.n_tiles = L.n; a.qtile = 1;
+    // no window bounds the context: few sequences with long contexts would leave most SMs without a CTA, so the
+    // keys of a (sequence, key / value head) pair are cut into ranges.  The count depends on the number of
+    // sequences only (a captured step replays with the same grid whatever the lengths have become)
+    const int pairs = L.n * s.kv_heads;
+    if (pairs <= w.att_split_pairs && pairs < 2 * h->sm_count) {
+      a.n_split = std::min(WINATTN_MAX_SPLIT, std::max(1, 2 * h->sm_count / pairs));
+      a.split_ws = w.att_split; a.split_cnt = w.att_split_cnt;
+    }
   }
   {
     ProfScope ps(h, NVLLM_K_ROPE_KV,

@@ -188,6 +188,10 @@ struct Workspace {
   // vector [T, side_p] act dtype
   float *m2_xbc = nullptr, *m2_dtx = nullptr, *m2_decay = nullptr, *v_first = nullptr;
   void* side_g = nullptr;
+  // attention decode over split key ranges: partial states and arrival counters (WinAttnArgs::split_ws / split_cnt)
+  float* att_split = nullptr;
+  unsigned* att_split_cnt = nullptr;
+  int att_split_pairs = 0;  // (sequence, key / value head) pairs the two buffers hold
   float* moe_Y = nullptr;  // [T k, H]
   float* moe_y = nullptr;  // [T, H]
   void* moe_xs = nullptr;  // [T k, H] bf16: normed activations in expert-sorted order

@@ -432,6 +432,7 @@ cudaError_t launch_softcap(cudaStream_t st, const float* p, int S, size_t stride
 // ---------------------------------------------------------------- attention_window.cu
 // Grouped-query attention over a sliding window of the paged cache, optional softmax sink,
 // optional unweighted RMS norm of q / k per head; every size is a run-time argument.
+constexpr int WINATTN_MAX_SPLIT = 16;  // key ranges per (sequence, key / value head) of a decode step
 struct WinAttnArgs {
   int T, n_seqs;
   int H, G, dim, vdim;   // query heads, key / value heads, query-key and value entries per head
@@ -473,6 +474,12 @@ struct WinAttnArgs {
   float slope_exp;
   const float* sink_w;          // [H]
   int gate_head;
+  // decode over long contexts: the keys of a (sequence, key / value head) are cut into n_split ranges, one CTA
+  // each; their partial states meet in split_ws [n_seqs][G][n_split][16][vdim + 2] floats, merged by the CTA
+  // that arrives last (split_cnt [n_seqs * G], zero between launches).  n_split <= 1: one CTA per pair
+  int n_split;
+  float* split_ws;
+  unsigned* split_cnt;
 };
 cudaError_t launch_winattn_prep(cudaStream_t st, int qdt, int kvdt, const WinAttnArgs& a);
 // Projection epilogue of an attention whose q, k, v pass a short causal convolution over time:

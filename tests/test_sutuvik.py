@@ -596,6 +596,30 @@ def test_the_correction_chooses_and_the_plain_scores_weigh(prec):
         eng.close()
 
 
+@gpu
+def test_decoding_with_the_keys_of_a_long_context_cut_into_ranges():
+    """bf16, tensor-core head sizes, three sequences of 900, 300 and 5 tokens decoding together: a
+    decode step cuts the keys of each (sequence, key / value head) into ranges that separate CTAs
+    read, some of them empty for the short sequences; the sink must join the merged state once."""
+    j = model([layer(att(heads=4, kv_heads=2, dim=64, vdim=64, every=100)), layer(att2(heads=8, kv_heads=2, dim=128, vdim=64, rot_dims=64)),
+               layer(att(heads=2, kv_heads=2, dim=128, vdim=64, coef=0.0))], width=128, parts=2, side=8)
+    cfg, w, eng = setup(j, C.PREC_BF16, seed=31, num_blocks=8)
+    try:
+        lens = {"a": 900, "b": 300, "c": 5}
+        toks = {k: prompt(j, n + 12, 32 + i) for i, (k, n) in enumerate(lens.items())}
+        want = {k: ref.forward(j, w, t) for k, t in toks.items()}
+        eng.step([(k, toks[k][:n], []) for k, n in lens.items()])
+        rows = {k: [] for k in lens}
+        for t in range(12):
+            out, _ = eng.step([(k, [toks[k][n + t]], [0]) for k, n in lens.items()], decode=True)
+            for i, k in enumerate(lens):
+                rows[k].append(out[i])
+        for k, n in lens.items():
+            check(np.stack(rows[k]), want[k][n:], C.PREC_BF16, f"sequence {k}")
+    finally:
+        eng.close()
+
+
 # ------------------------------------------------------------------ GPU: models drawn at random
 def draw_model(rng):
     """Sizes, head counts, layer order, constants and which options exist at all are drawn."""
