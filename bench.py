@@ -670,11 +670,10 @@ def sutuvik_device_weights(cfg, device, seed=1234):
 
 
 # width 1024, 24 layers like Granite-MoE-1B: 16 Mamba-2 layers (32 heads of 64, state 128, 4 taps) and 8 attention
-# layers (16 heads over 4 K / V heads of 64 values; keys of 64 in the biased kind, of 128 with 64 rotated in the
-# other); 32 gated experts of 512 in 4 groups, 8 per token from the best 2 groups (Granite's expert sizes);
+# layers (16 heads of 64 over 4 K / V heads, in the rotated kind 32 entries rotated); 32 gated experts of 512 in 4 groups, 8 per token from the best 2 groups (Granite's expert sizes);
 # norms in 2 parts, 4 taps on the mixers' input, 64 token-input entries per layer.
 def _su():
-    return sutuvik_cfg(1024, 24, 49155, 32, 64, 128, 1, 4, 16, 4, 64, 64, 128, 32, 8, 512, 4, 2, 2, 4, 64)
+    return sutuvik_cfg(1024, 24, 49155, 32, 64, 128, 1, 4, 16, 4, 64, 64, 64, 32, 8, 512, 4, 2, 2, 4, 64)
 
 
 SUTUVIK_SIZES = {

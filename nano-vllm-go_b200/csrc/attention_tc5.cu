@@ -6,6 +6,12 @@
 // the scheduler's block tables, the cached prefix of a sequence (NumCachedTokens) attended but
 // not recomputed.
 //
+// Options (AttnArgs, compiled in by the OPT template flag): a sink in the softmax's denominator (score 0 or
+// learned per head) and the output of a head times a gate per (token, head) — both outside the per-score
+// loop.  Capped scores and distance penalties stay with the mma.sync kernels of attention_window.cu: a
+// transform of every score in the softmax warps (tried: 3.5 to 5.7 ms against 0.97 ms plain, 16 x 4096 tokens,
+// 16 heads of 64) made this kernel slower than those.
+//
 // One CTA = 128 queries of one sequence x one query head; the SM holds two such CTAs, so that
 // one's softmax runs under the other's MMAs.  Per key tile j (BN keys):
 //   TMA warp      K_j / V_j tiles of the paged pool (one (block, kv head) slab is contiguous;
@@ -58,7 +64,8 @@ __device__ __forceinline__ float ex2(float x) {
 
 }  // namespace
 
-template <int HD>
+// OPT: the options of AttnArgs (sink, gate per head) are compiled in
+template <int HD, bool OPT>
 __global__ void __launch_bounds__(PT_THREADS, 2)
 attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                         const __grid_constant__ CUtensorMap tmV, AttnArgs a, Trace tr) {
@@ -198,7 +205,8 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     const int q = warp;  // TMEM lane quadrant of this warp
     const int r = q * 32 + lane;
     const int qpos = start + q0 + r;
-    const float sl2 = a.scale * 1.4426950408889634f;
+    constexpr float LOG2E = 1.4426950408889634f;
+    const float sl2 = a.scale * LOG2E;
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
     // O accumulates in TMEM across the key tiles (the P V MMAs run with accumulate = 1).  The
     // exponent reference m_used only follows the running maximum when it has grown by more than
@@ -280,7 +288,10 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     // n_tiles - 1 now and the parity test below can only pass on the last tile's completion.
     mbar_wait(b_ofull, (n_tiles - 1) & 1);
     tc_fence_after();
-    const float inv = 1.0f / l_run;
+    if (OPT && a.sink && m_used > -INFINITY)  // the sink: a term of the denominator without key or value
+      l_run += ex2((a.sink_w ? a.sink_w[head] : 0.f) * LOG2E - m_used * sl2);
+    float inv = 1.0f / l_run;
+    if (OPT && a.head_gate && r < rows_valid) inv *= a.head_gate[(size_t)(row0 + q0 + r) * a.gate_ld + head];
     bf16* op = (bf16*)a.out + (size_t)(row0 + q0 + r) * a.nh * HD + (size_t)head * HD;
 #pragma unroll 1
     for (int c0 = 0; c0 < HD; c0 += 32) {
@@ -313,7 +324,7 @@ bool attn_prefill_tc5_enabled() {
   return on;
 }
 
-template <int HD>
+template <int HD, bool OPT>
 static cudaError_t prefill_tc5_launch(cudaStream_t st, const AttnArgs& a) {
   using Cf = PtCfg<HD>;
   const int pool_rows = a.pool_blocks * a.nkv * KV_BLOCK;
@@ -323,12 +334,12 @@ static cudaError_t prefill_tc5_launch(cudaStream_t st, const AttnArgs& a) {
   if (!tq || !tk || !tv) return cudaErrorInvalidValue;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc5_kernel<HD>,
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc5_kernel<HD, OPT>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cf::SMEM);
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
-  (void)launch_k(attn_prefill_tc5_kernel<HD>, dim3(a.n_qtiles, a.nh), dim3(PT_THREADS), Cf::SMEM, st,
+  (void)launch_k(attn_prefill_tc5_kernel<HD, OPT>, dim3(a.n_qtiles, a.nh), dim3(PT_THREADS), Cf::SMEM, st,
                  *reinterpret_cast<const CUtensorMap*>(tq), *reinterpret_cast<const CUtensorMap*>(tk),
                  *reinterpret_cast<const CUtensorMap*>(tv), a, next_trace(13));
   return cudaGetLastError();
@@ -338,7 +349,9 @@ static cudaError_t prefill_tc5_launch(cudaStream_t st, const AttnArgs& a) {
 cudaError_t launch_attn_prefill_tc5(cudaStream_t st, const AttnArgs& a) {
   if (a.n_qtiles <= 0) return cudaSuccess;
   if (a.pool_blocks <= 0 || a.total_rows <= 0) return cudaErrorInvalidValue;
-  return a.hd == 64 ? prefill_tc5_launch<64>(st, a) : prefill_tc5_launch<128>(st, a);
+  if (a.sink || a.head_gate)
+    return a.hd == 64 ? prefill_tc5_launch<64, true>(st, a) : prefill_tc5_launch<128, true>(st, a);
+  return a.hd == 64 ? prefill_tc5_launch<64, false>(st, a) : prefill_tc5_launch<128, false>(st, a);
 }
 
 }  // namespace nvllm

@@ -47,7 +47,7 @@ __device__ __forceinline__ int first_key(const WinAttnArgs& a, int i) {
 template <bool FAST>
 __device__ __forceinline__ float cap_score(float s, float cap) {
   if (!FAST) return cap * tanhf(s / cap);
-  const float x = __fdividef(s, cap);
+  const float x = s * __fdividef(1.0f, cap);  // the reciprocal leaves the loop over the scores
   const float e = __expf(-2.0f * fabsf(x));
   return copysignf(cap * __fdividef(1.0f - e, 1.0f + e), x);
 }

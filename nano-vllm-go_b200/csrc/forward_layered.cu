@@ -926,7 +926,15 @@ static int ffn_moe_relu2(nvllm_handle* h, const ListedLayer& y, Pending* p1, Pen
   return run_gemm(h, w.hbuf, ff, y.w2, T, H, ff, 1.f, w.ws_b, w.ws_b_floats, H, p2);
 }
 
-// Grouped-query attention over the whole cached prefix with the options of the spec (attention_window.cu)
+// Prefill steps of an attention layer whose keys and values have one size, 64 or 128, in bf16, and whose scores are
+// neither capped nor biased by the distance (a sink and head gates are fine) run on the tcgen05 kernel
+// (attention_tc5.cu, 128 queries per tile); everything else on the window kernels (attention_window.cu)
+static bool attention_on_tc5(const nvllm_handle* h, const nvllm_layer_spec& s) {
+  return h->adt == DT_BF16 && h->kvdt == DT_BF16 && s.dim == s.vdim && (s.dim == 64 || s.dim == 128) &&
+         s.softcap == 0.f && s.dist_slope == 0.f && attn_prefill_tc5_enabled();
+}
+
+// Grouped-query attention over the whole cached prefix with the options of the spec
 static int mixer_attention(nvllm_handle* h, const ListedLayer& y, int run_idx, Pending* out) {
   const StepLayout& L = h->lay;
   Workspace& w = h->ws;
@@ -986,7 +994,21 @@ static int mixer_attention(nvllm_handle* h, const ListedLayer& y, int run_idx, P
     ProfScope ps(h, L.prefill ? NVLLM_K_ATTN_PREFILL : NVLLM_K_ATTN_DECODE,
                  (double)L.sum_len * s.kv_heads * (s.dim + s.vdim) * kvsz, 2.0 * s.heads * (s.dim + s.vdim) * L.attn_pairs,
                  (double)T * (s.heads * s.dim + y.ov_p) * asz);
-    LAUNCH(h, launch_winattn(h->stream, h->adt, h->kvdt, a));
+    if (L.prefill && h->attn_qtile == 128 && attention_on_tc5(h, s)) {
+      AttnArgs t{};
+      t.q = w.q; t.out = w.attn_out; t.qdt = h->adt; t.kvdt = h->kvdt;
+      t.kpool = a.kpool; t.vpool = a.vpool;
+      t.n_seqs = L.n; t.nh = s.heads; t.nkv = s.kv_heads; t.hd = s.dim; t.scale = s.scale;
+      t.block_tables = a.block_tables; t.max_blocks = a.max_blocks;
+      t.cu_q = a.cu_q; t.seq_start = a.seq_start; t.seq_len = a.seq_len;
+      t.tile_seq = a.tile_seq; t.tile_q0 = a.tile_q0; t.n_qtiles = L.n_qtiles;
+      t.pool_blocks = h->num_blocks; t.total_rows = T; t.sm_count = h->sm_count;
+      t.sink = s.sink; t.sink_w = a.sink_w;
+      t.head_gate = s.head_gate ? w.att_gate : nullptr; t.gate_ld = s.heads;
+      LAUNCH(h, launch_attn_prefill_tc5(h->stream, t));
+    } else {
+      LAUNCH(h, launch_winattn(h->stream, h->adt, h->kvdt, a));
+    }
   }
   return run_gemm(h, w.attn_out, y.ov_p, y.w_o, T, H, y.ov_p, 1.f, w.ws_b, w.ws_b_floats, H, out);
 }
@@ -1574,7 +1596,8 @@ extern "C" int nvllm_create_layered(const nvllm_layered_config* c, const nvllm_l
             h->ropes.push_back(rt);
           }
         }
-        const int qt = winattn_qtile(h->adt, h->kvdt, s.dim, s.vdim);
+        // (a model whose attention layers all fit the tcgen05 kernel gets its tiles of 128 queries)
+        const int qt = attention_on_tc5(h, s) ? 128 : winattn_qtile(h->adt, h->kvdt, s.dim, s.vdim);
         win_qtile = win_qtile ? std::min(win_qtile, qt) : qt;
         q_cols = std::max(q_cols, std::max(y.n_q, y.ov_p));
       } else {

@@ -354,6 +354,11 @@ struct AttnArgs {
   // stream-K decode (attention_mma.cu): ticket per (seq, kv head, head chunk), zero between
   // kernels; total_tiles = host LOWER bound of the key tiles in the step (caps the grid)
   int* tickets;        // unused (stream-K experiment removed)
+  // options of the tcgen05 prefill kernel (all zero / null: plain causal softmax)
+  int sink;                // 1: the softmax denominator holds one more term, exp(sink_w[h]) (exp(0) without sink_w)
+  const float* sink_w;     // [nh] or null
+  const float* head_gate;  // [rows, gate_ld] or null: the output of (row, head) times head_gate[row * gate_ld + head]
+  int gate_ld;
   int pool_blocks;     // blocks in the layer's K / V pool (tensor-map extent)
   int total_rows;      // rows of q / out in this step (tensor-map extent; tcgen05 prefill kernel)
   int sm_count;

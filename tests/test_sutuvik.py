@@ -112,6 +112,17 @@ def mma_model():
                  width=128, parts=2, taps=4, side=16)
 
 
+def tc5_model():
+    """Keys and values of one size, 64, and scores neither capped nor biased by the distance in
+    every attention layer: in bf16 the prefill steps of such a model run on the tcgen05 attention
+    kernel with tiles of 128 queries (the sink joins there too)."""
+    return model([layer(att2(heads=4, kv_heads=2, dim=64, vdim=64, rot_dims=32, softcap=0.0), moe(ff=64)),
+                  layer(mam(heads=4, vdim=32, state=64, groups=1, norm_groups=4)),
+                  layer(att2(heads=8, kv_heads=2, dim=64, vdim=64, rot_dims=64, scaling=None, softcap=0.0),
+                        moe(ff=96, experts=4, top=1, count=2, keep=1)),
+                  layer(att2(heads=2, kv_heads=2, dim=64, vdim=64, rot_dims=0, softcap=0.0))], width=128, parts=2, taps=4, side=16)
+
+
 def random_weights(j, seed, bf16=False):
     cfg = C.sutuvik_from_json(j)
     rng = np.random.default_rng(seed)
@@ -248,6 +259,9 @@ CASES = {
     "attention_rotary": lambda: model([layer(att2(v_mix=False))], **BARE),
     "attention_rotary_plain": lambda: model([layer(att2(v_mix=False, rot_dims=0, softcap=0.0))], **BARE),
     "attention_rotary_all_entries": lambda: model([layer(att2(v_mix=False, rot_dims=16, scaling=None, base=50.0))], **BARE),
+    "attention_biased_heads_of_128": lambda: model([layer(att(heads=4, kv_heads=1, dim=128, vdim=128, v_mix=False, every=20))], **dict(BARE, width=128)),
+    "attention_rotary_heads_of_128": lambda: model([layer(att2(heads=2, kv_heads=2, dim=128, vdim=128, v_mix=False, rot_dims=96, softcap=0.0))], **dict(BARE, width=128)),
+    "attention_rotary_heads_of_64": lambda: model([layer(att2(heads=6, kv_heads=2, dim=64, vdim=64, v_mix=False, rot_dims=64, softcap=0.0))], **dict(BARE, width=128)),
     "value_mixing": lambda: model([layer(att()), layer(att2()), layer(att())], **BARE),
     "mamba2": lambda: model([layer(mam())], **BARE),
     "mamba2_one_group_wide_state": lambda: model([layer(mam(heads=2, vdim=40, state=200, groups=1, norm_groups=1, conv=3))], **BARE),
@@ -298,7 +312,7 @@ def test_residual_stream_after_every_layer():
             eng.close()
 
 
-MODELS = {"mixed": mixed_model, "odd": odd_model, "mma": mma_model}
+MODELS = {"mixed": mixed_model, "odd": odd_model, "mma": mma_model, "tc5": tc5_model}
 
 
 # ------------------------------------------------------------------ GPU: schedules
@@ -325,7 +339,7 @@ def test_prefill_equals_token_by_token_decoding(which, prec):
 
 @gpu
 @pytest.mark.parametrize("prec", PRECS)
-@pytest.mark.parametrize("which", ["mixed", "mma"])
+@pytest.mark.parametrize("which", ["mixed", "mma", "tc5"])
 def test_portions_of_several_sizes_down_to_two_tokens(which, prec):
     j = no_close_calls(MODELS[which](), prec)
     cfg, w, eng = setup(j, prec)
@@ -345,9 +359,9 @@ def test_portions_of_several_sizes_down_to_two_tokens(which, prec):
 
 
 @gpu
-@pytest.mark.parametrize("prec", PRECS)
-def test_batches_of_unequal_requests_equal_each_alone(prec):
-    j = no_close_calls(mma_model() if prec == C.PREC_BF16 else mixed_model(), prec)
+@pytest.mark.parametrize("which,prec", [("mixed", C.PREC_FP32), ("mma", C.PREC_BF16), ("tc5", C.PREC_BF16)])
+def test_batches_of_unequal_requests_equal_each_alone(which, prec):
+    j = no_close_calls(MODELS[which](), prec)
     cfg, w, eng = setup(j, prec, num_blocks=10)
     try:
         A, B, Cc, Dd = (prompt(j, n, s) for n, s in ((150, 4), (41, 5), (7, 6), (290, 7)))
@@ -389,7 +403,8 @@ def test_pages_and_slots_are_freed_and_used_again(prec):
 
 
 @gpu
-@pytest.mark.parametrize("which,prec", [("odd", C.PREC_FP32), ("mixed", C.PREC_FP32), ("mixed", C.PREC_BF16), ("mma", C.PREC_BF16)])
+@pytest.mark.parametrize("which,prec", [("odd", C.PREC_FP32), ("mixed", C.PREC_FP32), ("mixed", C.PREC_BF16), ("mma", C.PREC_BF16),
+                                        ("tc5", C.PREC_BF16)])
 def test_first_tokens_of_a_sequence(which, prec):
     """Positions 0, 1, 2: shorter than the convolutions and any tile; a one-token prompt (its only
     key shares the softmax with the sink); the convolutions read zeros before the start and the
@@ -457,7 +472,8 @@ def test_a_far_key_among_hundreds(kind, prec):
     if kind == "biased":
         mk, n = (lambda: layer(att(heads=8, kv_heads=2, dim=d, vdim=d, v_mix=False, every=50))), 330
     else:
-        mk, n = (lambda: layer(att2(heads=2, kv_heads=1, dim=d, vdim=d, v_mix=False, rot_dims=8))), 880
+        # (bf16: uncapped scores, the tcgen05 prefill kernel)
+        mk, n = (lambda: layer(att2(heads=2, kv_heads=1, dim=d, vdim=d, v_mix=False, rot_dims=8, softcap=0.0 if d == 64 else 6.0))), 880
     j = model([mk(), mk()], width=64, parts=2, side=0)
     cfg, w = random_weights(j, 14, bf16=prec == C.PREC_BF16)
     make_standout(w, [("l0.mix.v", slice(None))], 400.0)
@@ -520,10 +536,11 @@ def test_a_sink_that_outweighs_every_key(kind, prec):
     sink of score zero beside scores that a small scale keeps far below it for the first tokens.
     Left out, counted per key, scaled or biased, the read-out would be several times too large
     (the logits, which also hold the token's own embedding, move by a tenth of their range)."""
+    d = 64 if prec == C.PREC_BF16 else 16  # bf16: the tensor-core kernels' sizes
     if kind == "learned":
-        j = model([layer(att(heads=4, kv_heads=2, v_mix=False, scale=0.02))], **BARE)
+        j = model([layer(att(heads=4, kv_heads=2, dim=d, vdim=d, v_mix=False, scale=0.02))], **BARE)
     else:
-        j = model([layer(att2(heads=4, kv_heads=2, v_mix=False, scale=0.02))], **BARE)
+        j = model([layer(att2(heads=4, kv_heads=2, dim=d, vdim=d, v_mix=False, scale=0.02, softcap=0.0 if d == 64 else 6.0))], **BARE)
     cfg, w = random_weights(j, 16, bf16=prec == C.PREC_BF16)
     if kind == "learned":
         w["l0.mix.sink"][:] = np.array([4.0, 3.0, 5.0, -2.0], dtype=np.float32)
