@@ -1037,6 +1037,21 @@ static int mixer_mamba2(nvllm_handle* h, const ListedLayer& y, const LayerRun& r
   m.state_pool = h->state_pool; m.slot_floats = h->state_slot_floats; m.tail_off = r.tail_off;
   m.xbc = w.m2_xbc; m.dtx = w.m2_dtx; m.decay = w.m2_decay; m.o = w.lr_o;
   m.out = w.attn_out; m.o_ld = y.ov_p;
+  m.state_off = r.state_off;
+  if (mamba2_slot_decode_ok(m)) {
+    // one row per sequence: convolution, step sizes and the recurrence as one launch.  Algorithmic bytes: every
+    // sequence's state once in and once out, the row's inputs, the read-outs
+    {
+      ProfScope ps(h, NVLLM_K_RECUR, (double)L.n * inner * s.state * 8 + (double)T * ((ch + s.heads) * 4 + 2.0 * inner * 4),
+                   4.0 * T * inner * s.state, (double)T * y.n_in * 4 * (pin.S - 1) + (double)T * ch * 4 * (s.conv - 1));
+      LAUNCH(h, launch_mamba2_slot_decode(h->stream, m, w.lr_o));
+    }
+    {
+      ProfScope ps(h, NVLLM_K_RECUR, (double)T * inner * (4 + 4 + 4 + asz), 0, (double)T * inner * 4 * (pin.S - 1));
+      LAUNCH(h, launch_mamba2_slot_out(h->stream, h->adt, m));
+    }
+    return run_gemm(h, w.attn_out, y.ov_p, y.w_o, T, H, y.ov_p, 1.f, w.ws_b, w.ws_b_floats, H, out);
+  }
   {
     ProfScope ps(h, NVLLM_K_RECUR, (double)T * ((ch + s.heads) * 4 + (ch + inner + s.heads) * 4), 0,
                  (double)T * y.n_in * 4 * (pin.S - 1) + (double)T * ch * 4 * (s.conv - 1));

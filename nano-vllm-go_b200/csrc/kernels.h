@@ -632,6 +632,7 @@ struct Mamba2SlotArgs {
   const float *conv_w, *conv_b, *dt_bias, *a_log, *d_skip, *norm_w;  // [ch, taps], [ch], [heads] x 3, [inner]
   const int *cu_q, *positions, *state_slots;
   const float* state_pool; size_t slot_floats, tail_off;  // tail [taps - 1][ch] inside a slot
+  size_t state_off;             // the layer's state [heads][N][vdim] inside a slot (the fused decode kernel)
   float* xbc;     // [T, ch]   silu(conv + bias): x | B | C
   float* dtx;     // [T, inner] dt * x (the scan's values)
   float* decay;   // [T, heads]
@@ -640,6 +641,9 @@ struct Mamba2SlotArgs {
 };
 cudaError_t launch_mamba2_slot_prep(cudaStream_t st, const Mamba2SlotArgs& a);
 cudaError_t launch_mamba2_slot_out(cudaStream_t st, int odt, const Mamba2SlotArgs& a);
+// One row per sequence: prep and the recurrence as one launch, a CTA per (sequence, head); o [T, inner] read-outs
+bool mamba2_slot_decode_ok(const Mamba2SlotArgs& a);
+cudaError_t launch_mamba2_slot_decode(cudaStream_t st, const Mamba2SlotArgs& a, float* o);
 cudaError_t launch_mamba_scan(cudaStream_t st, const MambaArgs& a);
 cudaError_t launch_mamba_gate_norm(cudaStream_t st, const MambaArgs& a, int odt, void* out);
 

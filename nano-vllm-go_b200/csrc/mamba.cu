@@ -256,6 +256,138 @@ __global__ void __launch_bounds__(256) mamba2_slot_out_kernel(Mamba2SlotArgs a, 
   TRACE_EXIT(tr);
 }
 
+// Steps with one row per sequence: convolution, step size, decay and the recurrence of a (sequence, head)
+// pair as ONE launch (mamba2_slot_prep_kernel and the scan of linrec.cu in one).  CTA = (sequence, head), 256
+// threads.  Phase 1: the head's step size and decay; the convolution (+ bias, SiLU) of the head's vdim
+// channels of x and of its group's N channels of B and of C into shared memory (the x channels also to xbc,
+// where mamba2_slot_out_kernel reads them for the D skip).  Phase 2: the head's state [N][vdim] goes once
+// through the registers, VW columns per thread and 256 / (vdim / VW) rows in flight:
+// S <- decay S + B_n (dt x_p), y_p += S C_n, written back in place; the rows' partial read-outs meet in shared
+// memory.  A sequence at position 0 starts from zeros whatever the slot holds.
+// VW = 4: 16-byte loads and stores (vdim a multiple of 4); VW = 1 otherwise.
+constexpr int M2D_THREADS = 256;
+template <int TAPS, int VW>
+__global__ void __launch_bounds__(M2D_THREADS) mamba2_slot_decode_kernel(Mamba2SlotArgs a, float* __restrict__ o, Trace tr) {
+  TRACE_ENTRY(tr);
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int MT = TAPS > 0 ? TAPS : 8;
+  const int taps = TAPS > 0 ? TAPS : a.taps;
+  const int t = blockIdx.x, hh = blockIdx.y;
+  const int P = a.vdim, N = a.N;
+  const int inner = a.heads * P, gn = a.G * N, ch = inner + 2 * gn;
+  const int g = hh / (a.heads / a.G);
+  extern __shared__ __align__(16) float m2d_smem[];
+  float* xs = m2d_smem;       // [P]  dt * silu(conv x)
+  float* Bs = xs + ((P + 3) & ~3);  // [N]
+  float* Cs = Bs + N;         // [N]
+  float* red = Cs + N;        // [rows in flight][P]
+  __shared__ float s_dt, s_decay;
+  if (threadIdx.x == 0) {
+    const float z = sum_slices(a.in_p + (size_t)t * a.in_ld + inner + ch + hh, a.in_S, a.in_stride) + a.dt_bias[hh];
+    const float dt = z > 20.f ? z : log1pf(expf(z));
+    s_dt = dt;
+    s_decay = expf(-expf(a.a_log[hh]) * dt);
+  }
+  const int pos = a.positions[t], keep = taps - 1;
+  const float* tail = a.state_pool + (size_t)a.state_slots[t] * a.slot_floats + a.tail_off;
+  const float* cur = a.in_p + (size_t)t * a.in_ld + inner;
+  __syncthreads();
+  const float dt = s_dt, decay = s_decay;
+  // the head's P + 2 N convolution channels
+  for (int i = threadIdx.x; i < P + 2 * N; i += blockDim.x) {
+    const int c = i < P ? hh * P + i : (i < P + N ? inner + g * N + (i - P) : inner + gn + g * N + (i - P - N));
+    float y = a.conv_b ? a.conv_b[c] : 0.f;
+#pragma unroll
+    for (int j = 0; j < MT; j++) {
+      if (j >= taps) continue;
+      const int back = keep - j;  // the input `back` positions before this token
+      float u = 0.f;
+      if (back == 0) u = a.in_S == 1 ? cur[c] : sum_slices(cur + c, a.in_S, a.in_stride);
+      else if (back <= pos) u = tail[(size_t)(keep - back) * ch + c];
+      y = fmaf(a.conv_w[(size_t)c * taps + j], u, y);
+    }
+    const float v = a.fast_act ? __fdividef(y, 1.0f + __expf(-y)) : silu(y);
+    if (i < P) {
+      xs[i] = v * dt;
+      a.xbc[(size_t)t * ch + c] = v;
+    } else if (i < P + N) {
+      Bs[i - P] = v;
+    } else {
+      Cs[i - P - N] = v;
+    }
+  }
+  __syncthreads();
+  // the recurrence
+  const int cols = P / VW;                       // column units of VW
+  const int rows_par = M2D_THREADS / cols;       // rows in flight (the launcher keeps cols <= 256)
+  const int u = threadIdx.x % cols, rg = threadIdx.x / cols;
+  float* state = const_cast<float*>(a.state_pool) + (size_t)a.state_slots[t] * a.slot_floats + a.state_off + (size_t)hh * N * P;
+  const bool has_prev = pos > 0;
+  float acc[VW], xv[VW];
+#pragma unroll
+  for (int e = 0; e < VW; e++) { acc[e] = 0.f; xv[e] = xs[u * VW + e]; }
+  if (rg < rows_par) {
+#pragma unroll 4
+    for (int n = rg; n < N; n += rows_par) {
+      float* sp = state + (size_t)n * P + u * VW;
+      float sv[VW];
+      if (VW == 4) {
+        const float4 q4 = has_prev ? *reinterpret_cast<const float4*>(sp) : make_float4(0.f, 0.f, 0.f, 0.f);
+        sv[0] = q4.x; sv[1 % VW] = q4.y; sv[2 % VW] = q4.z; sv[3 % VW] = q4.w;
+      } else {
+        sv[0] = has_prev ? sp[0] : 0.f;
+      }
+      const float bn = Bs[n], cn = Cs[n];
+#pragma unroll
+      for (int e = 0; e < VW; e++) {
+        sv[e] = fmaf(decay, sv[e], bn * xv[e]);
+        acc[e] = fmaf(sv[e], cn, acc[e]);
+      }
+      if (VW == 4) *reinterpret_cast<float4*>(sp) = make_float4(sv[0], sv[1 % VW], sv[2 % VW], sv[3 % VW]);
+      else sp[0] = sv[0];
+    }
+#pragma unroll
+    for (int e = 0; e < VW; e++) red[(size_t)rg * P + u * VW + e] = acc[e];
+  }
+  __syncthreads();
+  for (int p = threadIdx.x; p < P; p += blockDim.x) {
+    float y = 0.f;
+    for (int r = 0; r < rows_par; r++) y += red[(size_t)r * P + p];
+    o[(size_t)t * inner + hh * P + p] = y;
+  }
+  TRACE_EXIT(tr);
+}
+
+bool mamba2_slot_decode_ok(const Mamba2SlotArgs& a) {
+  static const bool on = !(getenv("NVLLM_MAMBA2_DECODE_FUSED") && atoi(getenv("NVLLM_MAMBA2_DECODE_FUSED")) == 0);
+  const int cols = a.vdim % 4 == 0 ? a.vdim / 4 : a.vdim;
+  return on && a.T == a.n_seqs && cols <= M2D_THREADS && a.taps >= 1 && a.taps <= 8 && a.heads % a.G == 0;
+}
+
+// o: [T, inner] read-outs (what the scan would have written); a.state_off: the layer's state inside a slot
+cudaError_t launch_mamba2_slot_decode(cudaStream_t st, const Mamba2SlotArgs& a, float* o) {
+  if (a.T <= 0) return cudaSuccess;
+  if (!mamba2_slot_decode_ok(a)) return cudaErrorInvalidValue;
+  const bool v4 = a.vdim % 4 == 0;
+  const int cols = v4 ? a.vdim / 4 : a.vdim;
+  const size_t smem = ((size_t)((a.vdim + 3) & ~3) + 2 * a.N + (size_t)(M2D_THREADS / cols) * a.vdim) * sizeof(float);
+  const dim3 grid(a.T, a.heads);
+#define M2D(TP_, VW_)                                                                                               \
+  {                                                                                                                  \
+    if (smem > 48 * 1024)                                                                                            \
+      cudaFuncSetAttribute(mamba2_slot_decode_kernel<TP_, VW_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    (void)launch_k(mamba2_slot_decode_kernel<TP_, VW_>, grid, dim3(M2D_THREADS), smem, st, a, o, next_trace(21));     \
+  }
+  if (v4) {
+    if (a.taps == 4) M2D(4, 4) else if (a.taps == 3) M2D(3, 4) else if (a.taps == 2) M2D(2, 4) else M2D(0, 4)
+  } else {
+    M2D(0, 1)
+  }
+#undef M2D
+  return cudaGetLastError();
+}
+
 cudaError_t launch_mamba2_slot_prep(cudaStream_t st, const Mamba2SlotArgs& a) {
   if (a.T <= 0) return cudaSuccess;
   if (a.taps < 1 || a.taps > 8 || a.heads > 256) return cudaErrorInvalidValue;
