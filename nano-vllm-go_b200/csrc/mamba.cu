@@ -163,6 +163,32 @@ mamba_gate_norm_kernel(MambaArgs a, OT* __restrict__ out, Trace tr) {
 //                            clamp), the head's decay exp(-exp(A_log) dt), and dt x (the scan's values)
 //   mamba2_slot_out_kernel   one CTA per token: y = read-out + D x, times silu(z), RMS norm in norm_groups
 //                            equal parts (eps of the model), times the weight -> act dtype
+// 16-byte accesses of the row kernels below: four neighbouring channels per thread
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 sum_slices4(const float* __restrict__ p, int S, size_t stride) {
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int s = 0; s < S; s++) {
+    const float4 v = ld4(p + (size_t)s * stride);
+    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+  }
+  return acc;
+}
+__device__ __forceinline__ void st4(float* p, float a, float b, float c, float d) {
+  *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void st4(bf16* p, float a, float b, float c, float d) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+  uint2 u;
+  u.x = *reinterpret_cast<uint32_t*>(&lo);
+  u.y = *reinterpret_cast<uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(p) = u;
+}
+// every row, segment and tail of the two kernels starts on a 16-byte boundary
+__device__ __forceinline__ bool m2_rows_aligned(const Mamba2SlotArgs& a) {
+  const int inner = a.heads * a.vdim, gn = a.G * a.N;
+  return (a.vdim % 4 == 0) && (gn % 4 == 0) && (a.in_ld % 4 == 0) && (a.in_stride % 4 == 0) && (inner % 4 == 0);
+}
+
 template <int TAPS>
 __global__ void __launch_bounds__(256) mamba2_slot_prep_kernel(Mamba2SlotArgs a, Trace tr) {
   TRACE_ENTRY(tr);
@@ -204,6 +230,35 @@ __global__ void __launch_bounds__(256) mamba2_slot_prep_kernel(Mamba2SlotArgs a,
     }
   }
   const bool one = a.in_S == 1;
+  if (TAPS == 4 && m2_rows_aligned(a)) {
+    // four channels per thread: their 16 taps are 64 contiguous bytes, every tap's inputs one 16-byte load
+    for (int c = threadIdx.x * 4; c < ch; c += blockDim.x * 4) {
+      float y[4], wv[4][4];
+#pragma unroll
+      for (int k = 0; k < 4; k++) {
+        const float4 w4 = ld4(a.conv_w + (size_t)(c + k) * 4);
+        wv[k][0] = w4.x; wv[k][1] = w4.y; wv[k][2] = w4.z; wv[k][3] = w4.w;
+        y[k] = a.conv_b ? a.conv_b[c + k] : 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        if (!src[j]) continue;  // before the sequence's start: zeros
+        const float4 u = (one || !part[j]) ? ld4(src[j] + c) : sum_slices4(src[j] + c, a.in_S, a.in_stride);
+        y[0] = fmaf(wv[0][j], u.x, y[0]); y[1] = fmaf(wv[1][j], u.y, y[1]);
+        y[2] = fmaf(wv[2][j], u.z, y[2]); y[3] = fmaf(wv[3][j], u.w, y[3]);
+      }
+      float v[4];
+#pragma unroll
+      for (int k = 0; k < 4; k++) v[k] = a.fast_act ? __fdividef(y[k], 1.0f + __expf(-y[k])) : silu(y[k]);
+      st4(a.xbc + (size_t)t * ch + c, v[0], v[1], v[2], v[3]);
+      if (c < inner) {
+        const float dt = s_dt[c / a.vdim];
+        st4(a.dtx + (size_t)t * inner + c, v[0] * dt, v[1] * dt, v[2] * dt, v[3] * dt);
+      }
+    }
+    TRACE_EXIT(tr);
+    return;
+  }
   for (int c = threadIdx.x; c < ch; c += blockDim.x) {
     float u[MT], wv[MT];
 #pragma unroll
@@ -227,18 +282,32 @@ __global__ void __launch_bounds__(256) mamba2_slot_out_kernel(Mamba2SlotArgs a, 
   TRACE_ENTRY(tr);
   pdl_launch_dependents();
   pdl_wait();
-  extern __shared__ float row[];
+  extern __shared__ __align__(16) float row[];
   __shared__ float ginv[64];
   const int t = blockIdx.x;
   const int inner = a.heads * a.vdim, ch = inner + 2 * a.G * a.N;
-  for (int i = threadIdx.x; i < inner; i += blockDim.x) {
-    const float z = sum_slices(a.in_p + (size_t)t * a.in_ld + i, a.in_S, a.in_stride);
-    const float x = a.xbc[(size_t)t * ch + i];
-    const float y = a.o[(size_t)t * inner + i] + a.d_skip[i / a.vdim] * x;
-    row[i] = y * (a.fast_act ? __fdividef(z, 1.0f + __expf(-z)) : silu(z));
+  const int part = inner / a.norm_groups;
+  const bool vec = m2_rows_aligned(a);
+  if (vec) {
+    for (int i = threadIdx.x * 4; i < inner; i += blockDim.x * 4) {
+      const float4 z = sum_slices4(a.in_p + (size_t)t * a.in_ld + i, a.in_S, a.in_stride);
+      const float4 x = ld4(a.xbc + (size_t)t * ch + i);
+      const float4 o = ld4(a.o + (size_t)t * inner + i);
+      const float d = a.d_skip[i / a.vdim];
+      const float zz[4] = {z.x, z.y, z.z, z.w};
+      const float yy[4] = {o.x + d * x.x, o.y + d * x.y, o.z + d * x.z, o.w + d * x.w};
+#pragma unroll
+      for (int k = 0; k < 4; k++) row[i + k] = yy[k] * (a.fast_act ? __fdividef(zz[k], 1.0f + __expf(-zz[k])) : silu(zz[k]));
+    }
+  } else {
+    for (int i = threadIdx.x; i < inner; i += blockDim.x) {
+      const float z = sum_slices(a.in_p + (size_t)t * a.in_ld + i, a.in_S, a.in_stride);
+      const float x = a.xbc[(size_t)t * ch + i];
+      const float y = a.o[(size_t)t * inner + i] + a.d_skip[i / a.vdim] * x;
+      row[i] = y * (a.fast_act ? __fdividef(z, 1.0f + __expf(-z)) : silu(z));
+    }
   }
   __syncthreads();
-  const int part = inner / a.norm_groups;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   for (int g = warp; g < a.norm_groups; g += nw) {
     float sq = 0.f;
@@ -251,8 +320,20 @@ __global__ void __launch_bounds__(256) mamba2_slot_out_kernel(Mamba2SlotArgs a, 
   }
   __syncthreads();
   OT* op = (OT*)a.out + (size_t)t * a.o_ld;
-  for (int i = threadIdx.x; i < a.o_ld; i += blockDim.x)
-    op[i] = from_f32<OT>(i < inner ? row[i] * ginv[i / part] * a.norm_w[i] : 0.f);
+  if (vec && part % 4 == 0 && a.o_ld % 4 == 0) {
+    for (int i = threadIdx.x * 4; i < a.o_ld; i += blockDim.x * 4) {
+      if (i < inner) {  // inner and o_ld are multiples of 4: a quad is all inside or all padding
+        const float4 r4 = ld4(row + i), w4 = ld4(a.norm_w + i);
+        const float gi = ginv[i / part];
+        st4(op + i, r4.x * gi * w4.x, r4.y * gi * w4.y, r4.z * gi * w4.z, r4.w * gi * w4.w);
+      } else {
+        st4(op + i, 0.f, 0.f, 0.f, 0.f);
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < a.o_ld; i += blockDim.x)
+      op[i] = from_f32<OT>(i < inner ? row[i] * ginv[i / part] * a.norm_w[i] : 0.f);
+  }
   TRACE_EXIT(tr);
 }
 
