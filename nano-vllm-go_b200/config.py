@@ -770,8 +770,8 @@ def _sutuvik_layer(i: int, lc: dict) -> LayerSpec:
     m = lc["mixer"]
     kind = lc.get("type")
     if kind in ("attention", "attention_2"):
-        kw = dict(mixer=MIXER_ATTENTION, heads=int(m["heads"]), kv_heads=int(m["kv_heads"]), dim=int(m["dim"]),
-                  vdim=int(m["vdim"]), scale=float(m["scale"]), sink=1, v_mix=int(bool(m.get("v_mix"))))
+        kw = dict(mixer=MIXER_ATTENTION, heads=int(m["heads"]), kv_heads=int(m.get("kv_heads") or m["heads"]), dim=int(m["dim"]),
+                  vdim=int(m.get("vdim") or m["dim"]), scale=float(m["scale"]), sink=1, v_mix=int(bool(m.get("v_mix"))))
         if kind == "attention":
             qt = m.get("q_temp") or {}
             kw.update(qk_norm=3, dist_slope=SUTUVIK_SLOPE_EXPONENT, sink_learned=1, head_gate=1,
@@ -786,7 +786,7 @@ def _sutuvik_layer(i: int, lc: dict) -> LayerSpec:
                           rot_fast=float(sc["high"]), rot_slow=float(sc["low"]))
     elif kind == "mamba2":
         kw = dict(mixer=MIXER_MAMBA2, heads=int(m["heads"]), vdim=int(m["vdim"]), dim=int(m["state"]),
-                  state=int(m["state"]), ssm_groups=int(m["groups"]), norm_groups=int(m["norm_groups"]),
+                  state=int(m["state"]), ssm_groups=int(m.get("groups") or 1), norm_groups=int(m.get("norm_groups") or 1),
                   conv=int(m["conv"]))
     else:
         raise ValueError(f"layer {i}: unknown layer type {kind!r}")
